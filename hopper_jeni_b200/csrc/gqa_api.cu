@@ -1,0 +1,128 @@
+// C-ABI entry points: argument validation, workspace carve-up and the launch
+// sequence of each operator.  No allocation happens on the hot path (the forward
+// status word is created once per device on first use).
+#include "gqa_common.cuh"
+#include "gqa_kernels.cuh"
+
+namespace {
+
+using gqa::Shape;
+
+int check_device() {
+    static thread_local int cached_dev = -1;
+    static thread_local int cached_rc = GQA_OK;
+    int dev = 0;
+    GQA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev == cached_dev) return cached_rc;
+    int major = 0;
+    GQA_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    cached_dev = dev;
+    cached_rc = (major == 10) ? GQA_OK : GQA_ERR_ARCH;
+    return cached_rc;
+}
+
+int check_shape(int B, int Hq, int Hkv, int S, int D) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0) return GQA_ERR_BAD_ARGUMENT;
+    if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
+    if (S % 128 != 0 || Hq % Hkv != 0) return GQA_ERR_UNSUPPORTED;
+    if ((size_t)B * Hq * S >= (size_t)1 << 31) return GQA_ERR_UNSUPPORTED;  // TMA row coordinate is 32-bit
+    return GQA_OK;
+}
+
+}  // namespace
+
+extern "C" int gqa_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv, int S,
+                       int D, int causal, float scale, gqa_stream_t stream_) {
+    if (!Q || !K || !V || !O) return GQA_ERR_BAD_ARGUMENT;
+    int rc = check_shape(B, Hq, Hkv, S, D);
+    if (rc) return rc;
+    if (!gqa::aligned16(Q) || !gqa::aligned16(K) || !gqa::aligned16(V) || !gqa::aligned16(O) ||
+        (LSE && !gqa::aligned16(LSE)))
+        return GQA_ERR_BAD_ARGUMENT;
+    rc = check_device();
+    if (rc) return rc;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    unsigned int* status = nullptr;
+    rc = gqa::forward_status_word(&status);
+    if (rc) return rc;
+    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    return gqa::launch_fwd_sm100(Q, K, V, O, LSE, s, status, stream);
+}
+
+extern "C" int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv,
+                          int S, int D, int causal, float scale, gqa_stream_t stream) {
+    return gqa_fwd(Q, K, V, O, LSE, B, Hq, Hkv, S, D, causal, scale, stream);
+}
+
+extern "C" size_t gqa_bwd_workspace_bytes(int B, int Hq, int Hkv, int S, int D, int causal) {
+    (void)causal;
+    if (check_shape(B, Hq, Hkv, S, D) != GQA_OK) return 0;
+    const Shape s{B, Hq, Hkv, S, D, 0, 0.f};
+    return gqa::BwdWorkspace(s).total;
+}
+
+extern "C" int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
+                       void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+                       void* workspace, size_t workspace_bytes, gqa_stream_t stream_) {
+    if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV) return GQA_ERR_BAD_ARGUMENT;
+    int rc = check_shape(B, Hq, Hkv, S, D);
+    if (rc) return rc;
+    const void* ptrs[] = {Q, K, V, O, dO, LSE, dQ, dK, dV};
+    for (const void* p : ptrs)
+        if (!gqa::aligned16(p)) return GQA_ERR_BAD_ARGUMENT;
+    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    const gqa::BwdWorkspace ws(s);
+    if (!workspace || workspace_bytes < ws.total) return GQA_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GQA_ERR_BAD_ARGUMENT;
+    rc = check_device();
+    if (rc) return rc;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    char* w = static_cast<char*>(workspace);
+    unsigned int* status = reinterpret_cast<unsigned int*>(w + ws.status_off);
+    float* delta = reinterpret_cast<float*>(w + ws.delta_off);
+    float* lse2 = reinterpret_cast<float*>(w + ws.lse2_off);
+    float* dq_accum = reinterpret_cast<float*>(w + ws.dq_accum_off);
+
+    GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, stream));
+    rc = gqa::launch_bwd_preprocess(O, dO, LSE, delta, lse2, dq_accum, s.q_rows(), D, stream);
+    if (rc) return rc;
+    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse2, delta, dq_accum, dK, dV, s, status, stream);
+    if (rc) return rc;
+    return gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream);
+}
+
+extern "C" int gqa_check_status(const void* workspace, gqa_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const unsigned int* word = static_cast<const unsigned int*>(workspace);
+    if (!word) {
+        unsigned int* w = nullptr;
+        int rc = gqa::forward_status_word(&w);
+        if (rc) return rc;
+        word = w;
+    }
+    unsigned int host = 0;
+    GQA_CUDA_TRY(cudaMemcpyAsync(&host, word, sizeof host, cudaMemcpyDeviceToHost, stream));
+    GQA_CUDA_TRY(cudaStreamSynchronize(stream));
+    return host == 0 ? GQA_OK : gqa::note_device_timeout(host);
+}
+
+// ---- CUDA-core checker entry points (diagnostics; see gqa_simt.cu) ----------
+extern "C" int gqa_checker_fwd_simt(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq,
+                                    int Hkv, int S, int D, int causal, float scale, gqa_stream_t stream) {
+    if (!Q || !K || !V || !O) return GQA_ERR_BAD_ARGUMENT;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0 || D > 128 || Hq % Hkv) return GQA_ERR_UNSUPPORTED;
+    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    return gqa::launch_fwd_simt(Q, K, V, O, LSE, s, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gqa_checker_bwd_simt(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                                    const float* LSE, void* dQ, void* dK, void* dV, float* delta_scratch, int B,
+                                    int Hq, int Hkv, int S, int D, int causal, float scale, gqa_stream_t stream_) {
+    if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !delta_scratch) return GQA_ERR_BAD_ARGUMENT;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || (D != 64 && D != 128) || Hq % Hkv) return GQA_ERR_UNSUPPORTED;
+    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    int rc = gqa::launch_bwd_preprocess(O, dO, nullptr, delta_scratch, nullptr, nullptr, s.q_rows(), D, stream);
+    if (rc) return rc;
+    return gqa::launch_bwd_simt(Q, K, V, dO, LSE, delta_scratch, dQ, dK, dV, s, stream);
+}

@@ -1,0 +1,99 @@
+// Host-side services shared by every entry point: error text, launch counting,
+// tensor-map encoding through the driver entry point (no link-time libcuda
+// dependency), status strings.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "gqa_common.cuh"
+
+namespace gqa {
+
+static thread_local char g_err[512] = "";
+static std::atomic<unsigned long long> g_launches{0};
+
+int note_cuda_error(cudaError_t e, const char* what) {
+    snprintf(g_err, sizeof g_err, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+    return GQA_ERR_CUDA;
+}
+int note_driver_error(CUresult r, const char* what) {
+    snprintf(g_err, sizeof g_err, "%s: CUresult %d", what, (int)r);
+    return GQA_ERR_CUDA;
+}
+int note_device_timeout(unsigned int word) {
+    snprintf(g_err, sizeof g_err, "device status 0x%08x: wait site %u gave up in block %u", word, (word >> 20) & 0x7ffu,
+             word & 0xfffffu);
+    return GQA_ERR_DEVICE_TIMEOUT;
+}
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
+        return GQA_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * sizeof(__nv_bfloat16)};
+    cuuint32_t box[2] = {64u, box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled");
+    return GQA_OK;
+}
+
+int forward_status_word(unsigned int** out) {
+    constexpr int kMaxDev = 64;
+    static unsigned int* words[kMaxDev] = {};
+    static std::mutex mu;
+    int dev = 0;
+    GQA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDev) return GQA_ERR_BAD_ARGUMENT;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!words[dev]) {
+        unsigned int* p = nullptr;
+        GQA_CUDA_TRY(cudaMalloc(&p, 256));
+        GQA_CUDA_TRY(cudaMemset(p, 0, 256));
+        words[dev] = p;
+    }
+    *out = words[dev];
+    return GQA_OK;
+}
+
+}  // namespace gqa
+
+extern "C" const char* gqa_status_string(int status) {
+    switch (status) {
+        case GQA_OK: return "ok";
+        case GQA_ERR_BAD_ARGUMENT: return "bad argument (null, non-positive or misaligned)";
+        case GQA_ERR_UNSUPPORTED: return "unsupported shape (need D in {64,128}, S % 128 == 0, Hq % Hkv == 0)";
+        case GQA_ERR_WORKSPACE: return "workspace missing or too small";
+        case GQA_ERR_CUDA: return "CUDA call failed";
+        case GQA_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+        case GQA_ERR_ARCH: return "device is not compute capability 10.x";
+        default: return "unknown status";
+    }
+}
+extern "C" const char* gqa_last_cuda_error(void) { return gqa::g_err; }
+extern "C" unsigned long long gqa_launch_count(void) { return gqa::g_launches.load(); }
+extern "C" const char* gqa_version(void) { return "0.1"; }

@@ -1,0 +1,51 @@
+// Internal launcher declarations (one per kernel role).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace gqa {
+
+struct Shape {
+    int B, Hq, Hkv, S, D, causal;
+    float scale;
+    int G() const { return Hq / Hkv; }
+    size_t q_rows() const { return (size_t)B * Hq * S; }
+    size_t kv_rows() const { return (size_t)B * Hkv * S; }
+};
+
+// Workspace carve-up for the backward (offsets in bytes, 256-byte aligned).
+struct BwdWorkspace {
+    size_t status_off, delta_off, lse2_off, dq_accum_off, total;
+    explicit BwdWorkspace(const Shape& s) {
+        auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+        status_off = 0;
+        delta_off = 256;
+        lse2_off = delta_off + up(s.q_rows() * sizeof(float));
+        dq_accum_off = lse2_off + up(s.q_rows() * sizeof(float));
+        total = dq_accum_off + up(s.q_rows() * (size_t)s.D * sizeof(float));
+    }
+};
+
+// Stage 1 of the backward: Delta, LSE*log2(e), zeroed dQ accumulator.
+int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float* delta, float* lse2, float* dq_accum,
+                          size_t rows, int D, cudaStream_t stream);
+// Stage 3 of the backward: dQ = bf16(scale * dq_accum).
+int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream);
+
+// Tensor-core forward (tcgen05 + TMEM + TMA).
+int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
+                     unsigned int* status, cudaStream_t stream);
+// Stage 2 of the backward: KV-tile-parallel main kernel (tcgen05 + TMEM + TMA); dK/dV written
+// once per element, dQ accumulated into dq_accum with fp32 reductions.
+int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const float* lse2,
+                          const float* delta, float* dq_accum, void* dK, void* dV, const Shape& s,
+                          unsigned int* status, cudaStream_t stream);
+
+// CUDA-core checker kernels (slow, simple; fp32 math on bf16 inputs).
+int launch_fwd_simt(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
+                    cudaStream_t stream);
+int launch_bwd_simt(const void* Q, const void* K, const void* V, const void* dO, const float* LSE, const float* delta,
+                    void* dQ, void* dK, void* dV, const Shape& s, cudaStream_t stream);
+
+}  // namespace gqa

@@ -1,0 +1,119 @@
+// Memory-bound helper kernels around the tensor-core backward:
+//   * preprocess: Delta = rowsum(dO * O), LSE pre-multiplied by log2(e), and zeroing of
+//     the fp32 dQ accumulator, in one pass (stage 1 of the backward);
+//   * finalise:   dQ = bf16(scale * dq_accum) (stage 3).
+// Algorithmic traffic per query row (D bf16 elements): preprocess reads 2*D*2 B and writes
+// D*4 + 8 B; finalise reads D*4 B and writes D*2 B.
+#include "gqa_common.cuh"
+#include "gqa_kernels.cuh"
+
+namespace gqa {
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// One group of D/8 lanes per row; each lane owns 8 consecutive elements (one 16-byte load
+// from O and one from dO).  A warp covers 256/D rows per step.
+template <int D>
+__global__ void __launch_bounds__(256)
+bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO, const float* __restrict__ lse,
+                      float* __restrict__ delta, float* __restrict__ lse2, float4* __restrict__ dq_accum,
+                      size_t rows) {
+    constexpr int kLanesPerRow = D / 8;
+    constexpr int kRowsPerWarp = 32 / kLanesPerRow;
+    const int lane = threadIdx.x & 31;
+    const size_t warp_global = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const size_t n_warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    const int sub = lane / kLanesPerRow, part = lane % kLanesPerRow;
+    for (size_t base = warp_global * kRowsPerWarp; base < rows; base += n_warps * kRowsPerWarp) {
+        const size_t row = base + sub;
+        float acc = 0.f;
+        if (row < rows) {
+            const uint4 a = O[row * kLanesPerRow + part];
+            const uint4 b = dO[row * kLanesPerRow + part];
+            const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc = fmaf(__uint_as_float(av[i] << 16), __uint_as_float(bv[i] << 16), acc);
+                acc = fmaf(__uint_as_float(av[i] & 0xffff0000u), __uint_as_float(bv[i] & 0xffff0000u), acc);
+            }
+            if (dq_accum) {
+                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                dq_accum[(row * kLanesPerRow + part) * 2 + 0] = z;
+                dq_accum[(row * kLanesPerRow + part) * 2 + 1] = z;
+            }
+        }
+#pragma unroll
+        for (int off = kLanesPerRow / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (row < rows && part == 0) {
+            delta[row] = acc;
+            if (lse2) lse2[row] = lse[row] * kLog2e;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+dq_finalise_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, size_t n8, float scale) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 a = acc[2 * i], b = acc[2 * i + 1];
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * scale, a.y * scale);
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(a.z * scale, a.w * scale);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x * scale, b.y * scale);
+        __nv_bfloat162 p3 = __floats2bfloat162_rn(b.z * scale, b.w * scale);
+        uint4 o;
+        o.x = *reinterpret_cast<uint32_t*>(&p0);
+        o.y = *reinterpret_cast<uint32_t*>(&p1);
+        o.z = *reinterpret_cast<uint32_t*>(&p2);
+        o.w = *reinterpret_cast<uint32_t*>(&p3);
+        dq[i] = o;
+    }
+}
+
+int grid_for(size_t work_items, int per_block) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    size_t want = (work_items + per_block - 1) / per_block;
+    size_t cap = (size_t)sms * 16;  // a multiple of the SM count; grid-stride loops cover the rest
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    return (int)want;
+}
+
+}  // namespace
+
+int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float* delta, float* lse2, float* dq_accum,
+                          size_t rows, int D, cudaStream_t stream) {
+    const int rows_per_block = (256 / 32) * (256 / D);
+    const int grid = grid_for(rows, rows_per_block);
+    if (D == 64)
+        bwd_preprocess_kernel<64><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
+                                                            lse, delta, lse2, reinterpret_cast<float4*>(dq_accum), rows);
+    else
+        bwd_preprocess_kernel<128><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
+                                                             lse, delta, lse2, reinterpret_cast<float4*>(dq_accum), rows);
+    count_launch();
+    GQA_CUDA_TRY(cudaGetLastError());
+    return GQA_OK;
+}
+
+int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream) {
+    const size_t n8 = elems / 8;
+    const int grid = grid_for(n8, 256);
+    dq_finalise_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(dq_accum), static_cast<uint4*>(dQ), n8,
+                                                 scale);
+    count_launch();
+    GQA_CUDA_TRY(cudaGetLastError());
+    return GQA_OK;
+}
+
+}  // namespace gqa
+
+extern "C" int gqa_bwd_delta(const void* O, const void* dO, float* delta, size_t rows, int D, gqa_stream_t stream) {
+    if (!O || !dO || !delta || rows == 0) return GQA_ERR_BAD_ARGUMENT;
+    if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
+    if (!gqa::aligned16(O) || !gqa::aligned16(dO)) return GQA_ERR_BAD_ARGUMENT;
+    return gqa::launch_bwd_preprocess(O, dO, nullptr, delta, nullptr, nullptr, rows, D,
+                                      reinterpret_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,144 @@
+"""Tensor-level wrappers over the C ABI.
+
+torch is used only for device memory and streams; all arithmetic happens inside the library.
+Layouts follow the reference launchers (src/attention/GQA_bwd_baseline.cu:549-554,
+src/attention/GQA_fwd_ref.cu:631-634): Q/O/dO/dQ ``[B,Hq,S,D]``, K/V/dK/dV ``[B,Hkv,S,D]`` bf16
+contiguous, LSE ``[B,Hq,S]`` fp32 (natural log).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import capi
+
+
+def _stream_ptr(stream=None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return int(s.cuda_stream)
+
+
+def _req(t: torch.Tensor, name: str, dtype) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _dims(q, k):
+    B, Hq, S, D = q.shape
+    if k.shape[0] != B or k.shape[2] != S or k.shape[3] != D:
+        raise ValueError(f"K/V shape {tuple(k.shape)} does not match Q {tuple(q.shape)}")
+    return B, Hq, k.shape[1], S, D
+
+
+def launch_count() -> int:
+    """Kernels launched by the library since it was loaded."""
+    return int(capi.load_library().gqa_launch_count())
+
+
+def gqa_forward(q, k, v, causal: bool = False, scale: float | None = None, out=None, lse=None, stream=None):
+    """O, LSE = attention(Q, K, V).  Mirrors ``launch_gqa_v62`` with D and causal as arguments."""
+    lib = capi.load_library()
+    for t, n in ((q, "Q"), (k, "K"), (v, "V")):
+        _req(t, n, torch.bfloat16)
+    B, Hq, Hkv, S, D = _dims(q, k)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    out = torch.empty_like(q) if out is None else out
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device) if lse is None else lse
+    _req(out, "O", torch.bfloat16)
+    _req(lse, "LSE", torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.gqa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                         B, Hq, Hkv, S, D, int(bool(causal)), scale, _stream_ptr(stream))
+    capi.check("gqa_fwd", rc)
+    return out, lse
+
+
+def bwd_workspace_bytes(B, Hq, Hkv, S, D, causal=False) -> int:
+    return int(capi.load_library().gqa_bwd_workspace_bytes(B, Hq, Hkv, S, D, int(bool(causal))))
+
+
+def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None = None,
+                 workspace=None, dq=None, dk=None, dv=None, stream=None):
+    """dQ, dK, dV.  Mirrors ``launch_gqa_backward_vj1d`` (G derived from the head counts)."""
+    lib = capi.load_library()
+    for t, n in ((q, "Q"), (k, "K"), (v, "V"), (o, "O"), (do, "dO")):
+        _req(t, n, torch.bfloat16)
+    _req(lse, "LSE", torch.float32)
+    B, Hq, Hkv, S, D = _dims(q, k)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    need = bwd_workspace_bytes(B, Hq, Hkv, S, D, causal)
+    if need == 0:
+        capi.check("gqa_bwd_workspace_bytes", -2)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    with torch.cuda.device(q.device):
+        rc = lib.gqa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,
+                         workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream_ptr(stream))
+    capi.check("gqa_bwd", rc)
+    return dq, dk, dv
+
+
+def gqa_delta(o, do, stream=None):
+    """Delta = rowsum(dO * O) (stage 1 of the backward on its own)."""
+    lib = capi.load_library()
+    _req(o, "O", torch.bfloat16)
+    _req(do, "dO", torch.bfloat16)
+    D = o.shape[-1]
+    rows = o.numel() // D
+    out = torch.empty(o.shape[:-1], dtype=torch.float32, device=o.device)
+    with torch.cuda.device(o.device):
+        rc = lib.gqa_bwd_delta(o.data_ptr(), do.data_ptr(), out.data_ptr(), rows, D, _stream_ptr(stream))
+    capi.check("gqa_bwd_delta", rc)
+    return out
+
+
+def check_status(workspace=None, stream=None) -> None:
+    """Raise if a bounded device-side wait gave up in the last forward (``workspace=None``) or backward."""
+    lib = capi.load_library()
+    rc = lib.gqa_check_status(workspace.data_ptr() if workspace is not None else None, _stream_ptr(stream))
+    capi.check("gqa_check_status", rc)
+
+
+def checker_forward(q, k, v, causal=False, scale=None):
+    """CUDA-core checker forward (diagnostics; slow)."""
+    lib = capi.load_library()
+    B, Hq, Hkv, S, D = _dims(q, k)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    out = torch.empty_like(q)
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    rc = lib.gqa_checker_fwd_simt(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                  B, Hq, Hkv, S, D, int(bool(causal)), scale, _stream_ptr())
+    capi.check("gqa_checker_fwd_simt", rc)
+    return out, lse
+
+
+def checker_backward(q, k, v, o, do, lse, causal=False, scale=None):
+    """CUDA-core checker backward (diagnostics; slow)."""
+    lib = capi.load_library()
+    B, Hq, Hkv, S, D = _dims(q, k)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    scratch = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    rc = lib.gqa_checker_bwd_simt(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(),
+                                  lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
+                                  B, Hq, Hkv, S, D, int(bool(causal)), scale, _stream_ptr())
+    capi.check("gqa_checker_bwd_simt", rc)
+    return dq, dk, dv
+
+
+def selftest_umma(x, y, n: int, mode: int, use_tma: bool):
+    """Run the UMMA building-block self test; returns C [128, n] fp32."""
+    lib = capi.load_library()
+    c = torch.empty((128, n), dtype=torch.float32, device=x.device)
+    rc = lib.gqa_selftest_umma(x.data_ptr(), y.data_ptr(), c.data_ptr(), n, mode, int(use_tma), _stream_ptr())
+    capi.check("gqa_selftest_umma", rc)
+    return c

@@ -1,0 +1,141 @@
+/*
+ * gqa.h -- C ABI of the Blackwell (sm_100a) grouped-query-attention library.
+ *
+ * Every entry point takes plain device pointers and sizes; nothing here depends
+ * on a framework.  Tensor contract (same as the reference launchers):
+ *   Q, O, dO, dQ : [B, Hq,  S, D]  bf16, contiguous, row-major
+ *   K, V, dK, dV : [B, Hkv, S, D]  bf16, contiguous, row-major
+ *   LSE          : [B, Hq, S]      fp32, natural log of sum_j exp(scale * q_i . k_j)
+ *   query head hq reads KV head hq / (Hq / Hkv)
+ * Supported: D in {64, 128}, S a multiple of 128, Hq a multiple of Hkv, all
+ * pointers 16-byte aligned.  Anything else returns an error code; the library
+ * never exits the process and never traps the device.
+ *
+ * All functions return GQA_OK (0) or a negative gqa_status.  Work is enqueued
+ * on `stream`; the functions do not synchronise it unless stated.
+ */
+#ifndef GQA_B200_H_
+#define GQA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* gqa_stream_t; /* same handle as cudaStream_t */
+
+typedef enum gqa_status {
+    GQA_OK = 0,
+    GQA_ERR_BAD_ARGUMENT = -1,   /* null pointer, non-positive size, misaligned pointer */
+    GQA_ERR_UNSUPPORTED = -2,    /* shape outside the supported set (D, S % 128, Hq % Hkv) */
+    GQA_ERR_WORKSPACE = -3,      /* workspace missing or smaller than gqa_bwd_workspace_bytes() */
+    GQA_ERR_CUDA = -4,           /* a CUDA runtime/driver call failed (see gqa_last_cuda_error) */
+    GQA_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up; outputs are invalid */
+    GQA_ERR_ARCH = -6            /* the current device is not compute capability 10.x */
+} gqa_status;
+
+/*
+ * Forward: O = softmax(scale * Q K^T [+ causal mask]) V and LSE.
+ * Replaces launch_gqa_v62(Q,K,V,O,LSE,B,Hq,Hkv,S,scale,stream)
+ * (src/attention/GQA_fwd_ref.cu:631-651), with D and causal made runtime arguments.
+ * LSE may be NULL when the caller does not need it.
+ */
+int gqa_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE,
+            int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+            gqa_stream_t stream);
+
+/*
+ * Alias of gqa_fwd under the entry name the reference's Python harness loads from a
+ * user-supplied shared object (harness/competitors.py:396-415, entry="launch_gqa").
+ */
+int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE,
+               int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+               gqa_stream_t stream);
+
+/*
+ * Bytes of device scratch gqa_bwd needs for this shape (Delta, the fp32 dQ
+ * accumulator and a status word).  The reference keeps the same buffers as
+ * function-static allocations inside its launcher
+ * (src/attention/GQA_bwd_baseline.cu:579-587); here the caller owns them.
+ */
+size_t gqa_bwd_workspace_bytes(int B, int Hq, int Hkv, int S, int D, int causal);
+
+/*
+ * Backward: dQ, dK, dV from Q, K, V, O, dO and LSE.
+ * Replaces launch_gqa_backward_vj1d<Br,Bc,D>(Q,K,V,O,dO,LSE,dQ,dK,dV,B,Hq,Hkv,G,S,scale)
+ * (src/attention/GQA_bwd_baseline.cu:549-602; the same argument list is used by every
+ * launcher in src/attention/GQA_bwd.cu).  G is derived as Hq / Hkv.
+ * `workspace` must be 256-byte aligned device memory of at least
+ * gqa_bwd_workspace_bytes(...) bytes; calls that share a workspace must not overlap.
+ * dK and dV are bit-reproducible from run to run; dQ is accumulated with fp32 atomics.
+ */
+int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+            const float* LSE, void* dQ, void* dK, void* dV,
+            int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+            void* workspace, size_t workspace_bytes, gqa_stream_t stream);
+
+/*
+ * Delta preprocess on its own: delta[r] = sum_d dO[r,d] * O[r,d] for `rows` rows.
+ * Replaces compute_drowsum_v22 (src/attention/GQA_bwd_baseline.cu:273-298).
+ */
+int gqa_bwd_delta(const void* O, const void* dO, float* delta, size_t rows, int D,
+                  gqa_stream_t stream);
+
+/*
+ * Reads the status word a previous gqa_fwd/gqa_bwd left on the device and returns
+ * GQA_OK or GQA_ERR_DEVICE_TIMEOUT.  Synchronises `stream`.  For gqa_bwd pass the
+ * same workspace; for gqa_fwd pass NULL (the forward uses a library-owned word).
+ */
+int gqa_check_status(const void* workspace, gqa_stream_t stream);
+
+/* Human-readable text for a gqa_status. */
+const char* gqa_status_string(int status);
+
+/* Text of the last CUDA error or device-timeout report this library saw on the calling thread ("" if none). */
+const char* gqa_last_cuda_error(void);
+
+/* Kernels launched by this library since load (all entry points, all threads). */
+unsigned long long gqa_launch_count(void);
+
+/* Library version, "major.minor". */
+const char* gqa_version(void);
+
+/*
+ * Building-block self test: one 128 x N x 128 bf16 UMMA product from two
+ * 128 x 128 bf16 matrices X and Y (row-major) into C[128, N] fp32.
+ *   mode 0: C = X  * Y^T   (A K-major,  B K-major)
+ *   mode 1: C = X  * Y     (A K-major,  B MN-major)
+ *   mode 2: C = X^T * Y^T  (A MN-major, B K-major)
+ *   mode 3: C = X^T * Y    (A MN-major, B MN-major)
+ *   mode 4: C = X  * Y^T   (A from tensor memory, B K-major)
+ *   mode 5: C = X  * Y     (A from tensor memory, B MN-major)
+ * N is 64 or 128 (for N = 64 only the first 64 rows/columns of Y are used).
+ * use_tma != 0 stages X and Y with TMA tile loads, otherwise threads write the
+ * swizzled layout themselves.  Synchronises `stream`.  No counterpart in the
+ * reference (its kernels are wgmma-based); used by the test-suite only.
+ */
+int gqa_selftest_umma(const void* X, const void* Y, float* C, int N, int mode, int use_tma,
+                      gqa_stream_t stream);
+
+/*
+ * CUDA-core checker kernels (diagnostics): a slow, simple restatement of forward
+ * and backward on the device, used by the tests to cross-check the tensor-core
+ * kernels at sizes where the CPU oracle takes too long.  No product entry point
+ * dispatches to them.  Same tensor contract as above, any S, D <= 128;
+ * `delta_scratch` is B*Hq*S floats of device memory.  They follow the reference's
+ * per-head loops (precision/baseline_gqa.py:169-197).
+ */
+int gqa_checker_fwd_simt(const void* Q, const void* K, const void* V, void* O, float* LSE,
+                         int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+                         gqa_stream_t stream);
+int gqa_checker_bwd_simt(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                         const float* LSE, void* dQ, void* dK, void* dV, float* delta_scratch,
+                         int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+                         gqa_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GQA_B200_H_ */

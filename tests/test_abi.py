@@ -1,0 +1,78 @@
+"""CPU tests of the drop-in boundary: the library loads, exports every symbol include/gqa.h declares,
+and rejects bad arguments with status codes before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from hopper_jeni_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "gqa.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gqa_[a-z0-9_]+|launch_gqa)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    assert _declared_symbols() == sorted(capi.EXPORTS)
+
+
+def test_library_exports_every_declared_symbol(gqa_lib):
+    for name in _declared_symbols():
+        assert hasattr(gqa_lib, name), name
+
+
+def test_version_and_status_strings(gqa_lib):
+    assert gqa_lib.gqa_version().decode().count(".") == 1
+    for code in range(0, -7, -1):
+        assert gqa_lib.gqa_status_string(code)
+    assert gqa_lib.gqa_status_string(-99).decode() == "unknown status"
+
+
+def test_workspace_bytes_formula(gqa_lib):
+    B, Hq, Hkv, S, D = 8, 12, 4, 4096, 64
+    rows = B * Hq * S
+    need = gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, D, 0)
+    assert need >= rows * D * 4 + 2 * rows * 4 + 256
+    assert need % 256 == 0
+    # unsupported shapes report zero
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 96, 0) == 0
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S + 64, D, 0) == 0
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, 10, 4, S, D, 0) == 0
+
+
+def test_argument_validation_needs_no_device(gqa_lib):
+    p = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
+    assert gqa_lib.gqa_fwd(None, p, p, p, None, 1, 4, 2, 128, 64, 0, 0.125, None) == -1
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 100, 64, 0, 0.125, None) == -2      # S % 128
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 128, 80, 0, 0.125, None) == -2      # D
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 5, 2, 128, 64, 0, 0.125, None) == -2      # Hq % Hkv
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 0, 4, 2, 128, 64, 0, 0.125, None) == -1      # B <= 0
+    mis = ctypes.c_void_p(4096 + 2)
+    assert gqa_lib.gqa_fwd(mis, p, p, p, None, 1, 4, 2, 128, 64, 0, 0.125, None) == -1    # misaligned
+    assert gqa_lib.gqa_bwd(p, p, p, p, p, p, p, p, p, 1, 4, 2, 128, 64, 0, 0.125, None, 0, None) == -3
+    assert gqa_lib.gqa_bwd(p, p, p, p, p, p, p, p, p, 1, 4, 2, 128, 64, 0, 0.125, p, 16, None) == -3
+    assert gqa_lib.gqa_bwd(p, p, p, p, p, None, p, p, p, 1, 4, 2, 128, 64, 0, 0.125, p, 1 << 30, None) == -1
+    assert gqa_lib.gqa_selftest_umma(p, p, p, 96, 0, 0, None) == -2
+    assert gqa_lib.gqa_bwd_delta(p, p, p, 16, 32, None) == -2
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setenv("GQA_B200_LIB", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(capi, "_LIB", None)
+    with pytest.raises(FileNotFoundError):
+        capi.load_library()
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+
+    import hopper_jeni_b200 as pkg
+
+    q = torch.zeros(1, 2, 128, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        pkg.gqa_forward(q, q, q)
