@@ -25,6 +25,8 @@ EXPORTS = {
     "launch_gqa": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "gqa_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "gqa_bwd_stage_times": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
+                                 _vp, ctypes.POINTER(ctypes.c_float)]),
     "gqa_bwd_delta": (_i, [_vp, _vp, _fp, _sz, _i, _vp]),
     "gqa_check_status": (_i, [_vp, _vp]),
     "gqa_status_string": (ctypes.c_char_p, [_i]),

@@ -61,9 +61,12 @@ extern "C" size_t gqa_bwd_workspace_bytes(int B, int Hq, int Hkv, int S, int D, 
     return gqa::BwdWorkspace(s).total;
 }
 
-extern "C" int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
-                       void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale,
-                       void* workspace, size_t workspace_bytes, gqa_stream_t stream_) {
+namespace {
+
+// Shared body of gqa_bwd and gqa_bwd_stage_times; `ev` is null or four events recorded around the stages.
+int run_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE, void* dQ,
+            void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale, void* workspace,
+            size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev) {
     if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
@@ -76,7 +79,6 @@ extern "C" int gqa_bwd(const void* Q, const void* K, const void* V, const void* 
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GQA_ERR_BAD_ARGUMENT;
     rc = check_device();
     if (rc) return rc;
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     char* w = static_cast<char*>(workspace);
     unsigned int* status = reinterpret_cast<unsigned int*>(w + ws.status_off);
     float* delta = reinterpret_cast<float*>(w + ws.delta_off);
@@ -84,11 +86,45 @@ extern "C" int gqa_bwd(const void* Q, const void* K, const void* V, const void* 
     float* dq_accum = reinterpret_cast<float*>(w + ws.dq_accum_off);
 
     GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, stream));
+    if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[0], stream));
     rc = gqa::launch_bwd_preprocess(O, dO, LSE, delta, lse2, dq_accum, s.q_rows(), D, stream);
     if (rc) return rc;
+    if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[1], stream));
     rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse2, delta, dq_accum, dK, dV, s, status, stream);
     if (rc) return rc;
-    return gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream);
+    if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[2], stream));
+    rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream);
+    if (rc) return rc;
+    if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[3], stream));
+    return GQA_OK;
+}
+
+}  // namespace
+
+extern "C" int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
+                       void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+                       void* workspace, size_t workspace_bytes, gqa_stream_t stream) {
+    return run_bwd(Q, K, V, O, dO, LSE, dQ, dK, dV, B, Hq, Hkv, S, D, causal, scale, workspace, workspace_bytes,
+                   reinterpret_cast<cudaStream_t>(stream), nullptr);
+}
+
+extern "C" int gqa_bwd_stage_times(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                                   const float* LSE, void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int S,
+                                   int D, int causal, float scale, void* workspace, size_t workspace_bytes,
+                                   gqa_stream_t stream_, float* stage_ms) {
+    if (!stage_ms) return GQA_ERR_BAD_ARGUMENT;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+    for (auto& e : ev) GQA_CUDA_TRY(cudaEventCreate(&e));
+    int rc = run_bwd(Q, K, V, O, dO, LSE, dQ, dK, dV, B, Hq, Hkv, S, D, causal, scale, workspace, workspace_bytes,
+                     stream, ev);
+    if (rc == GQA_OK) {
+        cudaError_t e = cudaEventSynchronize(ev[3]);
+        for (int i = 0; i < 3 && e == cudaSuccess; ++i) e = cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]);
+        if (e != cudaSuccess) rc = gqa::note_cuda_error(e, "stage timing");
+    }
+    for (auto& e : ev) cudaEventDestroy(e);
+    return rc;
 }
 
 extern "C" int gqa_check_status(const void* workspace, gqa_stream_t stream_) {

@@ -452,12 +452,8 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     if (rc) return rc;
     rc = make_panel_tmap(&mdo, dO, s.q_rows(), D, kTile);
     if (rc) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg::kSmemTotal));
-        attr_set = true;
-    }
+    GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg::kSmemTotal));
     BwdParams p;
     p.lse2 = lse2;
     p.delta = delta;

@@ -339,12 +339,8 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
     if (rc) return rc;
     rc = make_panel_tmap(&mv, V, s.kv_rows(), D, kTile);
     if (rc) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg::kSmemTotal));
-        attr_set = true;
-    }
+    GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg::kSmemTotal));
     FwdParams p;
     p.O = static_cast<__nv_bfloat16*>(O);
     p.LSE = LSE;

@@ -87,6 +87,24 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
     return dq, dk, dv
 
 
+def bwd_stage_times(q, k, v, o, do, lse, causal, scale, workspace, dq, dk, dv, flush=None):
+    """One backward with events around its stages; returns (preprocess_ms, main_ms, finalise_ms).
+    `flush`, if given, is overwritten first so the working set starts outside L2."""
+    import ctypes
+
+    lib = capi.load_library()
+    B, Hq, Hkv, S, D = _dims(q, k)
+    if flush is not None:
+        flush.zero_()
+    ms = (ctypes.c_float * 3)()
+    rc = lib.gqa_bwd_stage_times(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(),
+                                 lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D,
+                                 int(bool(causal)), float(scale), workspace.data_ptr(),
+                                 workspace.numel() * workspace.element_size(), _stream_ptr(), ms)
+    capi.check("gqa_bwd_stage_times", rc)
+    return float(ms[0]), float(ms[1]), float(ms[2])
+
+
 def gqa_delta(o, do, stream=None):
     """Delta = rowsum(dO * O) (stage 1 of the backward on its own)."""
     lib = capi.load_library()

@@ -77,6 +77,20 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
             void* workspace, size_t workspace_bytes, gqa_stream_t stream);
 
 /*
+ * gqa_bwd with CUDA events recorded on `stream` around its three stages.  Fills
+ * stage_ms[0..2] (host memory) with the device time of the Delta preprocess, the
+ * tensor-core main kernel and the dQ finalise, and synchronises the stream.  The
+ * reference times only the whole launcher (src/attention/GQA_bwd_baseline.cu:684-687);
+ * this entry point exists so that the roofline of the dominant kernel can be
+ * measured on the launching stream.
+ */
+int gqa_bwd_stage_times(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                        const float* LSE, void* dQ, void* dK, void* dV,
+                        int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+                        void* workspace, size_t workspace_bytes, gqa_stream_t stream,
+                        float* stage_ms);
+
+/*
  * Delta preprocess on its own: delta[r] = sum_d dO[r,d] * O[r,d] for `rows` rows.
  * Replaces compute_drowsum_v22 (src/attention/GQA_bwd_baseline.cu:273-298).
  */
