@@ -66,7 +66,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
@@ -148,8 +148,8 @@ def run_reference_arm(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -198,13 +198,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the clock sampler starts before the warm-up so that nvidia-smi is already reporting when the timed
+    # region begins; idle samples are dropped when it is read out
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     barrier()
     ops.check_status(ws)
 
     # ---- timed region: K steps, device-timed per step, L2 flushed before each ----
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = gqa.launch_count()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]

@@ -31,6 +31,20 @@ namespace {
 
 using namespace sm100;
 
+// Optional timeline tracing (development builds only): block 0 stamps clock64 at a few points per iteration.
+#ifdef GQA_BWD_TRACE
+__device__ long long g_bwd_trace[3][64][4];
+#define GQA_TRACE(role, it, slot)                                                              \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && (it) < 64 && (threadIdx.x & 31) == 0 && (((role) != 0) || warp == 4)) \
+            g_bwd_trace[role][it][slot] = clock64();                                           \
+    } while (0)
+#else
+#define GQA_TRACE(role, it, slot) \
+    do {                          \
+    } while (0)
+#endif
+
 constexpr int kTile = 128;
 constexpr int kPanel = kTile * 128;  // bytes of one 64-column panel of a 128-row tile
 constexpr int kBwdThreads = 448;
@@ -228,6 +242,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 // ---- dV += P^T dO(it): A = P^T in TMEM; query rows 0-63 sit in S columns [0,32), 64-127 in [64,96)
                 ok = mbar_wait(p_ready, it & 1, ctx, 23);
                 if (!ok) break;
+                GQA_TRACE(1, it, 0);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
@@ -248,6 +263,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 // ---- dK += dS^T Q(it)
                 ok = mbar_wait(ds_ready, it & 1, ctx, 25);
                 if (!ok) break;
+                GQA_TRACE(1, it, 1);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
@@ -261,6 +277,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);
                     if (!ok) break;
                     tc_fence_after_sync();
+                    GQA_TRACE(1, it, 2);
                 }
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
@@ -278,6 +295,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     tc_fence_after_sync();
                     issue_kmajor_pair(Cfg::kColDP, v_addr, do_addr + dn * Cfg::kTileBytes);
                     umma_commit(dp_full);
+                    GQA_TRACE(1, it, 3);
                 }
             }
             if (ok) umma_commit(acc_full);
@@ -289,6 +307,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         for (int it = 0; it < n_iter; ++it) {
             if (!mbar_wait(dq_full, it & 1, ctx, 40)) break;
             tc_fence_after_sync();
+            GQA_TRACE(2, it, 0);
             float* dst = p.dq_accum + ((size_t)q_row_of(it) + r) * D;
             if constexpr (D == 64) {
                 uint32_t v0[32], v1[32];
@@ -345,6 +364,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 29) && mbar_wait(s_full, it & 1, ctx, 30);
             if (!ok) break;
             tc_fence_after_sync();
+            GQA_TRACE(0, it, 0);
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
                 uint32_t v[32];
@@ -370,10 +390,12 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_ready);
+            GQA_TRACE(0, it, 1);
 
             ok = mbar_wait(dp_full, it & 1, ctx, 31);
             if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 32);
             if (!ok) break;
+            GQA_TRACE(0, it, 2);
             tc_fence_after_sync();
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
@@ -399,6 +421,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(ds_ready);
+            GQA_TRACE(0, it, 3);
         }
         // ---- epilogue: dV and scale*dK of this key row, half of the columns per warpgroup ----
         if (ok) ok = mbar_wait(acc_full, 0, ctx, 33);
@@ -477,6 +500,12 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
 }
 
 }  // namespace
+
+#ifdef GQA_BWD_TRACE
+extern "C" int gqa_debug_copy_bwd_trace(long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(g_bwd_trace));
+}
+#endif
 
 int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const float* lse2,
                           const float* delta, float* dq_accum, void* dK, void* dV, const Shape& s,

@@ -134,6 +134,14 @@ int gqa_selftest_umma(const void* X, const void* Y, float* C, int N, int mode, i
                       gqa_stream_t stream);
 
 /*
+ * Throughput probe over the same arrangements: reps x 8 back-to-back K = 16 products into one
+ * accumulator; *cycles_per_product receives the average SM cycles per product (host memory).
+ * C is scratch.  Synchronises `stream`.  No counterpart in the reference.
+ */
+int gqa_selftest_umma_cycles(const void* X, const void* Y, float* C, int N, int mode, int reps,
+                             float* cycles_per_product, gqa_stream_t stream);
+
+/*
  * CUDA-core checker kernels (diagnostics): a slow, simple restatement of forward
  * and backward on the device, used by the tests to cross-check the tensor-core
  * kernels at sizes where the CPU oracle takes too long.  No product entry point
