@@ -25,6 +25,8 @@ EXPORTS = {
     "launch_gqa": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "gqa_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "gqa_bwd_static_scratch_bytes": (_sz, []),
+    "gqa_bwd_static_scratch": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_bwd_stage_times": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
                                  _vp, ctypes.POINTER(ctypes.c_float)]),
     "gqa_bwd_delta": (_i, [_vp, _vp, _fp, _sz, _i, _vp]),
@@ -76,6 +78,6 @@ def check(fn: str, status: int) -> None:
     if status != GQA_OK:
         lib = load_library()
         detail = lib.gqa_status_string(status).decode()
-        if status in (-4, -5):
+        if status in (-3, -4, -5):
             detail += " | " + lib.gqa_last_cuda_error().decode()
         raise GqaError(fn, status, detail)

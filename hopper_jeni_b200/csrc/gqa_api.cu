@@ -1,6 +1,8 @@
 // C-ABI entry points: argument validation, workspace carve-up and the launch
 // sequence of each operator.  No allocation happens on the hot path (the forward
 // status word is created once per device on first use).
+#include <mutex>
+
 #include "gqa_common.cuh"
 #include "gqa_kernels.cuh"
 
@@ -75,7 +77,10 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
         if (!gqa::aligned16(p)) return GQA_ERR_BAD_ARGUMENT;
     const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
     const gqa::BwdWorkspace ws(s);
-    if (!workspace || workspace_bytes < ws.total) return GQA_ERR_WORKSPACE;
+    if (!workspace || workspace_bytes < ws.total) {
+        gqa::note_text("backward workspace: need %zu bytes, got %zu", ws.total, workspace ? workspace_bytes : (size_t)0);
+        return GQA_ERR_WORKSPACE;
+    }
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return GQA_ERR_BAD_ARGUMENT;
     rc = check_device();
     if (rc) return rc;
@@ -125,6 +130,59 @@ extern "C" int gqa_bwd_stage_times(const void* Q, const void* K, const void* V, 
     }
     for (auto& e : ev) cudaEventDestroy(e);
     return rc;
+}
+
+// ---- backward for callers that must not allocate --------------------------------------------
+// The scratch that gqa_bwd takes from its caller lives here in a fixed device array instead.
+// Every GPU that loads this library keeps these bytes resident until the process exits.
+#define GQA_STATIC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[GQA_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a kernel can use.
+// The device address is looked up once per device, with that device current, and cached.
+int static_scratch_address(void** out) {
+    constexpr int kMaxDev = 64;
+    static void* addr[kMaxDev] = {};
+    static std::mutex mu;
+    int dev = 0;
+    GQA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDev) return GQA_ERR_BAD_ARGUMENT;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void* p = nullptr;
+        GQA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) return GQA_ERR_CUDA;
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return GQA_OK;
+}
+
+}  // namespace
+
+extern "C" size_t gqa_bwd_static_scratch_bytes(void) { return GQA_STATIC_SCRATCH_BYTES; }
+
+extern "C" int gqa_bwd_static_scratch(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                                      const float* LSE, void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int S,
+                                      int D, int causal, float scale, gqa_stream_t stream) {
+    int rc = check_shape(B, Hq, Hkv, S, D);
+    if (rc) return rc;
+    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    const size_t need = gqa::BwdWorkspace(s).total;
+    if (need > GQA_STATIC_SCRATCH_BYTES) {
+        gqa::note_text("gqa_bwd_static_scratch: this shape needs %zu bytes of scratch, the built-in array holds %zu",
+                       need, (size_t)GQA_STATIC_SCRATCH_BYTES);
+        return GQA_ERR_WORKSPACE;
+    }
+    void* scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    // run_bwd clears the status word and the preprocess stage zeroes the dQ accumulator, so nothing
+    // left in the array by an earlier call is read.
+    return run_bwd(Q, K, V, O, dO, LSE, dQ, dK, dV, B, Hq, Hkv, S, D, causal, scale, scratch, need,
+                   reinterpret_cast<cudaStream_t>(stream), nullptr);
 }
 
 extern "C" int gqa_check_status(const void* workspace, gqa_stream_t stream_) {

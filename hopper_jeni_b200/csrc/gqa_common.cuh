@@ -15,6 +15,8 @@ namespace gqa {
 int note_cuda_error(cudaError_t e, const char* what);
 int note_driver_error(CUresult r, const char* what);
 void count_launch(unsigned n = 1);
+// printf-style text for gqa_last_cuda_error() (argument errors that deserve an explanation).
+void note_text(const char* fmt, ...);
 // Records which bounded wait gave up (decoded from the device status word); returns GQA_ERR_DEVICE_TIMEOUT.
 int note_device_timeout(unsigned int word);
 

@@ -2,6 +2,7 @@
 // tensor-map encoding through the driver entry point (no link-time libcuda
 // dependency), status strings.
 #include <atomic>
+#include <cstdarg>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -25,6 +26,12 @@ int note_device_timeout(unsigned int word) {
     snprintf(g_err, sizeof g_err, "device status 0x%08x: wait site %u gave up in block %u", word, (word >> 20) & 0x7ffu,
              word & 0xfffffu);
     return GQA_ERR_DEVICE_TIMEOUT;
+}
+void note_text(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
 }
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 

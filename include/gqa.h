@@ -77,6 +77,38 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
             void* workspace, size_t workspace_bytes, gqa_stream_t stream);
 
 /*
+ * Backward for callers that cannot allocate device memory.  No counterpart in the
+ * reference (its launcher grows function-static cudaMalloc buffers on demand).
+ *
+ * Some hosts of this library may not call cudaMalloc at the point where they need a
+ * backward pass: code running inside a framework's memory-planned region, a plugin that
+ * is handed only its input and output buffers, a real-time loop where an allocation
+ * could stall or fail.  gqa_bwd asks such a caller for a workspace it cannot provide.
+ * This variant takes its scratch (Delta, scaled LSE, the fp32 dQ accumulator, the status
+ * word) from one fixed array compiled into the library, gqa_bwd_static_scratch_bytes()
+ * = 32 MiB, resident on every GPU that loads the library until the process exits.  The
+ * caller still passes all inputs and outputs; results equal gqa_bwd's.
+ *
+ *  - Shapes whose scratch (gqa_bwd_workspace_bytes) exceeds the array are refused with
+ *    GQA_ERR_WORKSPACE and an explanation in gqa_last_cuda_error(); nothing is launched.
+ *    32 MiB covers e.g. B*Hq*S <= 126 976 rows at D = 64 or 64 512 rows at D = 128.
+ *  - It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *  - The first call on each device looks up the array's device address (one runtime
+ *    query, no allocation).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array, and it keeps what the last call left;
+ *    each call re-initialises the parts it reads, so back-to-back calls on one stream
+ *    are fine, but two calls that overlap on the GPU (different streams, or threads
+ *    without ordering) race on it and produce wrong gradients.
+ *  - gqa_check_status() cannot be pointed at the array; use gqa_bwd when the status
+ *    word matters.
+ */
+size_t gqa_bwd_static_scratch_bytes(void);
+int gqa_bwd_static_scratch(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                           const float* LSE, void* dQ, void* dK, void* dV,
+                           int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+                           gqa_stream_t stream);
+
+/*
  * gqa_bwd with CUDA events recorded on `stream` around its three stages.  Fills
  * stage_ms[0..2] (host memory) with the device time of the Delta preprocess, the
  * tensor-core main kernel and the dQ finalise, and synchronises the stream.  The
