@@ -14,9 +14,15 @@
 //   dV  += P^T dO      (A from TMEM,  B = dO panel read MN-major)
 //   dK  += dS^T Q      (A = dS^T K-major, B = Q panel read MN-major)
 //   dQ   = dS K        (A = dS^T read MN-major, B = K panel read MN-major)
-// Roles: warps 0-3 drain dQ, warps 4-7 / 8-11 are the two elementwise warpgroups
-// (each owns 64 query columns of the tile pair), warp 12 is the TMA producer and
-// warp 13 issues every UMMA.
+//
+// Roles (25 warps):
+//   warps 0-3    drain dQ tiles from TMEM into the fp32 accumulator
+//   warps 4-19   four elementwise warpgroups; each owns 32 query columns of the tile pair
+//   warp  20     TMA producer
+//   warps 21-24  UMMA issuers: [S^T, dP^T] | dV | dK | dQ
+// One warp can start a tcgen05.mma only about every 100 cycles whatever its shape, while
+// the tensor pipe needs 32-64 cycles for the products used here, so the five GEMMs are
+// issued by four warps in parallel; mbarriers carry every cross-warp dependency.
 //
 // Replaces gqa_bwd_vj1d (src/attention/GQA_bwd_baseline.cu:405-547) in the
 // G-loop-inside-the-CTA form of gqa_bwd_vz2_wgmma (src/attention/GQA_bwd.cu:15207-15342);
@@ -34,10 +40,9 @@ using namespace sm100;
 // Optional timeline tracing (development builds only): block 0 stamps clock64 at a few points per iteration.
 #ifdef GQA_BWD_TRACE
 __device__ long long g_bwd_trace[3][64][4];
-#define GQA_TRACE(role, it, slot)                                                              \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && (it) < 64 && (threadIdx.x & 31) == 0 && (((role) != 0) || warp == 4)) \
-            g_bwd_trace[role][it][slot] = clock64();                                           \
+#define GQA_TRACE(role, it, slot)                                                                  \
+    do {                                                                                           \
+        if (blockIdx.x == 0 && (it) < 64 && (threadIdx.x & 31) == 0) g_bwd_trace[role][it][slot] = clock64(); \
     } while (0)
 #else
 #define GQA_TRACE(role, it, slot) \
@@ -47,7 +52,10 @@ __device__ long long g_bwd_trace[3][64][4];
 
 constexpr int kTile = 128;
 constexpr int kPanel = kTile * 128;  // bytes of one 64-column panel of a 128-row tile
-constexpr int kBwdThreads = 448;
+constexpr int kBwdThreads = 800;
+constexpr int kWarpEw0 = 4, kWarpTma = 20, kWarpMmaS = 21, kWarpMmaDV = 22, kWarpMmaDK = 23,
+              kWarpMmaDQ = 24;
+constexpr int kEwThreads = 512;
 
 template <int D>
 struct BwdCfg {
@@ -61,17 +69,22 @@ struct BwdCfg {
     static constexpr int kOffQ = kOffV + kTileBytes;
     static constexpr int kOffDO = kOffQ + kQStages * kTileBytes;
     static constexpr int kOffDS = kOffDO + kDOStages * kTileBytes;
-    static constexpr int kOffLse = kOffDS + 2 * kPanel;
+    static constexpr int kOffDQ = kOffDS + 2 * kPanel;   // dQ staging: 4 drain warps x 2 boxes x (32 rows x 128 B)
+    static constexpr int kOffLse = kOffDQ + 4 * 2 * 4096;
     static constexpr int kOffDelta = kOffLse + kQStages * kVecBytes;
     static constexpr int kOffBars = kOffDelta + kQStages * kVecBytes;
-    static constexpr int kSmemTotal = 1024 + kOffBars + 256;
+    static constexpr int kSmemTotal = kOffBars + 256;  // the dynamic window must start 1024-byte aligned (checked)
     static constexpr uint32_t kTmemCols = 512;
+    // fp32 column map.  D = 64: every tile has its own columns.  D = 128: P^T overwrites the S^T columns
+    // and dQ reuses the dP^T columns; the p_free / dq_empty barriers guard the reuse.
+    static constexpr bool kPAliasesS = (D != 64);
+    static constexpr bool kDqAliasesDp = (D != 64);
     static constexpr uint32_t kColS = 0, kColDP = 128;
-    static constexpr uint32_t kColDQ = (D == 64) ? 256 : 128;  // D = 128: dQ reuses the dP columns
+    static constexpr uint32_t kColDQ = (D == 64) ? 256 : 128;
     static constexpr uint32_t kColDV = (D == 64) ? 320 : 256;
     static constexpr uint32_t kColDK = kColDV + D;
-    static constexpr bool kDqAliasesDp = (D != 64);
-    static_assert(kColDK + D <= 512, "TMEM budget");
+    static constexpr uint32_t kColP = (D == 64) ? 448 : 0;
+    static_assert(kColDK + D + (kPAliasesS ? 0 : 64) <= 512, "TMEM budget");
     static_assert(kSmemTotal <= 227 * 1024, "shared memory budget");
     static_assert(kSmemTotal > 114 * 1024, "one CTA per SM is assumed by the 512-column TMEM allocation");
 };
@@ -87,35 +100,48 @@ struct BwdParams {
     float scale, scale_log2;
 };
 
+// TMEM column of the bf16 P^T block that holds query columns [16*kk, 16*kk+16) (one K step of dV).
+template <int D>
+__device__ __forceinline__ uint32_t p_col_of_kstep(int kk) {
+    using Cfg = BwdCfg<D>;
+    if constexpr (Cfg::kPAliasesS) return Cfg::kColS + (kk >> 1) * 32 + (kk & 1) * 8;  // inside its owner's S columns
+    else return Cfg::kColP + kk * 8;
+}
+
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
-                     const BwdParams p) {
+                     const __grid_constant__ CUtensorMap mapDQ, const BwdParams p) {
     using Cfg = BwdCfg<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // swizzled panels need 1024-byte alignment; report instead of computing garbage
+        if (threadIdx.x == 0) atomicCAS(p.status, 0u, 0x80000000u | (99u << 20));
+        return;
+    }
     uint8_t* sK = smem + Cfg::kOffK;
     uint8_t* sV = smem + Cfg::kOffV;
     uint8_t* sQ = smem + Cfg::kOffQ;
     uint8_t* sDO = smem + Cfg::kOffDO;
     uint8_t* sDS = smem + Cfg::kOffDS;
+    uint8_t* sDQ = smem + Cfg::kOffDQ;
     float* sLse = reinterpret_cast<float*>(smem + Cfg::kOffLse);
     float* sDelta = reinterpret_cast<float*>(smem + Cfg::kOffDelta);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
-    uint64_t* kv_full = bars + 0;
-    uint64_t* s_full = bars + 1;
-    uint64_t* dp_full = bars + 2;
-    uint64_t* p_ready = bars + 3;
-    uint64_t* ds_ready = bars + 4;
-    uint64_t* ds_free = bars + 5;
-    uint64_t* dq_full = bars + 6;
-    uint64_t* dq_empty = bars + 7;
-    uint64_t* acc_full = bars + 8;
-    uint64_t* q_full = bars + 9;                     // [kQStages]
-    uint64_t* q_empty = q_full + Cfg::kQStages;      // [kQStages]
-    uint64_t* do_full = q_empty + Cfg::kQStages;     // [kDOStages]
-    uint64_t* do_empty = do_full + Cfg::kDOStages;   // [kDOStages]
+    uint64_t* kv_full = bars + 0;    // TMA: K and V tiles
+    uint64_t* s_full = bars + 1;     // issuer S   -> elementwise: S^T(it) complete
+    uint64_t* dp_full = bars + 2;    // issuer S   -> elementwise: dP^T(it) complete
+    uint64_t* p_ready = bars + 3;    // elementwise -> issuers: P^T(it) stored, S^T(it) consumed
+    uint64_t* ds_ready = bars + 4;   // elementwise -> issuers: dS^T(it) stored, dP^T(it) consumed
+    uint64_t* p_free = bars + 5;     // issuer dV  -> P^T(it) consumed
+    uint64_t* ds_free = bars + 6;    // issuers dK + dQ -> dS^T(it) consumed
+    uint64_t* dq_full = bars + 7;    // issuer dQ  -> drain warps
+    uint64_t* dq_empty = bars + 8;   // drain warps -> issuers: dQ columns free
+    uint64_t* acc_full = bars + 9;   // issuers dV + dK -> epilogue
+    uint64_t* q_full = bars + 10;                    // [kQStages] TMA: Q tile + LSE + Delta rows
+    uint64_t* q_empty = q_full + Cfg::kQStages;      // [kQStages] issuers S + dK
+    uint64_t* do_full = q_empty + Cfg::kQStages;     // [kDOStages] TMA: dO tile
+    uint64_t* do_empty = do_full + Cfg::kDOStages;   // [kDOStages] issuers S + dV
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(do_empty + Cfg::kDOStages);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
@@ -141,23 +167,24 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         mbar_init(kv_full, 1);
         mbar_init(s_full, 1);
         mbar_init(dp_full, 1);
-        mbar_init(p_ready, 256);
-        mbar_init(ds_ready, 256);
-        mbar_init(ds_free, 1);
+        mbar_init(p_ready, kEwThreads);
+        mbar_init(ds_ready, kEwThreads);
+        mbar_init(p_free, 1);
+        mbar_init(ds_free, 2);
         mbar_init(dq_full, 1);
         mbar_init(dq_empty, 128);
-        mbar_init(acc_full, 1);
+        mbar_init(acc_full, 2);
         for (int i = 0; i < Cfg::kQStages; ++i) {
             mbar_init(&q_full[i], 1);
-            mbar_init(&q_empty[i], 1);
+            mbar_init(&q_empty[i], 2);
         }
         for (int i = 0; i < Cfg::kDOStages; ++i) {
             mbar_init(&do_full[i], 1);
-            mbar_init(&do_empty[i], 1);
+            mbar_init(&do_empty[i], 2);
         }
         fence_mbar_init();
     }
-    if (warp == 13) {
+    if (warp == kWarpMmaS) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -165,14 +192,17 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ);
+    const uint32_t do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
 
-    if (warp == 12) {
+    if (warp == kWarpTma) {
         // ======================= TMA producer =======================
         if (elect_one()) {
             tma_prefetch_desc(&mapQ);
             tma_prefetch_desc(&mapK);
             tma_prefetch_desc(&mapV);
             tma_prefetch_desc(&mapDO);
+            tma_prefetch_desc(&mapDQ);
             mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
             for (int pn = 0; pn < Cfg::kPanels; ++pn) {
                 tma_load_2d(sK + pn * kPanel, &mapK, kv_full, pn * 64, kv_row0);
@@ -202,251 +232,255 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 }
             }
         }
-    } else if (warp == 13) {
-        // ======================= UMMA issuer =======================
-        if (elect_one()) {
-            const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);  // S^T, dP^T
-            const uint32_t idesc_dv = make_idesc_bf16(128, D, false, true);    // A K-major (TMEM or dS), B MN-major
-            const uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);     // A = dS^T read MN-major
-            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ);
-            const uint32_t do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
-            bool ok = true;
-
-            // S^T / dP^T: A = K or V tile (rows = keys), B = Q or dO tile (rows = queries), contraction over D
-            auto issue_kmajor_pair = [&](uint32_t col, uint32_t a0, uint32_t b0) {
+    } else if (warp == kWarpMmaS) {
+        // ======================= issuer: S^T(it) = K Q^T, dP^T(it) = V dO^T =======================
+        // The whole warp runs the loop (uniform control flow); `leader` marks the one lane that issues.
+        const uint32_t leader = elect_one() ? 1u : 0u;
+        const uint32_t idesc = make_idesc_bf16(128, 128, false, false);
+        auto issue = [&](uint32_t col, uint32_t a0, uint32_t b0) {
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kPanel + (kk & 3) * 32;
-                    umma_ss(tmem + col, make_sdesc_sw128(a0 + off, 16, 1024), make_sdesc_sw128(b0 + off, 16, 1024),
-                            idesc_s, kk > 0);
-                }
-            };
-
-            ok = mbar_wait(kv_full, 0, ctx, 20) && mbar_wait(&q_full[0], 0, ctx, 21);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_kmajor_pair(Cfg::kColS, k_addr, q_addr);
-                umma_commit(s_full);
-                ok = mbar_wait(&do_full[0], 0, ctx, 22);
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (kk >> 2) * kPanel + (kk & 3) * 32;
+                umma_ss_pred(leader, tmem + col, make_sdesc_sw128(a0 + off, 16, 1024),
+                             make_sdesc_sw128(b0 + off, 16, 1024), idesc, kk > 0);
             }
-            if (ok) {
-                tc_fence_after_sync();
-                issue_kmajor_pair(Cfg::kColDP, v_addr, do_addr);
-                umma_commit(dp_full);
-            }
-
-            for (int it = 0; it < n_iter && ok; ++it) {
-                const int qs = it % Cfg::kQStages, dos = it % Cfg::kDOStages;
-                const uint32_t q_cur = q_addr + qs * Cfg::kTileBytes, do_cur = do_addr + dos * Cfg::kTileBytes;
-                const bool more = it + 1 < n_iter;
-                // ---- dV += P^T dO(it): A = P^T in TMEM; query rows 0-63 sit in S columns [0,32), 64-127 in [64,96)
-                ok = mbar_wait(p_ready, it & 1, ctx, 23);
-                if (!ok) break;
-                GQA_TRACE(1, it, 0);
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t a_col = Cfg::kColS + (kk >> 2) * 64 + (kk & 3) * 8;
-                    umma_ts(tmem + Cfg::kColDV, tmem + a_col, make_sdesc_sw128(do_cur + kk * 2048, kPanel, 1024),
-                            idesc_dv, (it > 0 || kk > 0));
-                }
-                umma_commit(&do_empty[dos]);
-                // ---- S^T(it+1)
-                if (more) {
-                    const int qn = (it + 1) % Cfg::kQStages;
-                    ok = mbar_wait(&q_full[qn], ((it + 1) / Cfg::kQStages) & 1, ctx, 24);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_kmajor_pair(Cfg::kColS, k_addr, q_addr + qn * Cfg::kTileBytes);
-                    umma_commit(s_full);
-                }
-                // ---- dK += dS^T Q(it)
-                ok = mbar_wait(ds_ready, it & 1, ctx, 25);
-                if (!ok) break;
-                GQA_TRACE(1, it, 1);
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t a_off = (kk >> 2) * kPanel + (kk & 3) * 32;
-                    umma_ss(tmem + Cfg::kColDK, make_sdesc_sw128(ds_addr + a_off, 16, 1024),
-                            make_sdesc_sw128(q_cur + kk * 2048, kPanel, 1024), idesc_dv, (it > 0 || kk > 0));
-                }
-                umma_commit(&q_empty[qs]);
-                // ---- dQ(it) = dS K
-                if (it > 0) {
-                    ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    GQA_TRACE(1, it, 2);
-                }
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {
-                    umma_ss(tmem + Cfg::kColDQ, make_sdesc_sw128(ds_addr + kk * 2048, kPanel, 1024),
-                            make_sdesc_sw128(k_addr + kk * 2048, kPanel, 1024), idesc_dq, kk > 0);
-                }
-                umma_commit(dq_full);
-                umma_commit(ds_free);
-                // ---- dP^T(it+1)
-                if (more) {
-                    const int dn = (it + 1) % Cfg::kDOStages;
-                    ok = mbar_wait(&do_full[dn], ((it + 1) / Cfg::kDOStages) & 1, ctx, 27);
-                    if (ok && Cfg::kDqAliasesDp) ok = mbar_wait(dq_empty, it & 1, ctx, 28);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_kmajor_pair(Cfg::kColDP, v_addr, do_addr + dn * Cfg::kTileBytes);
-                    umma_commit(dp_full);
-                    GQA_TRACE(1, it, 3);
-                }
-            }
-            if (ok) umma_commit(acc_full);
+        };
+        bool ok = mbar_wait(kv_full, 0, ctx, 20);
+        for (int it = 0; it < n_iter && ok; ++it) {
+            const int qs = it % Cfg::kQStages, dos = it % Cfg::kDOStages;
+            ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 21);
+            if (ok && it > 0) ok = mbar_wait(p_ready, (it - 1) & 1, ctx, 22);                        // S^T columns read
+            if (ok && it > 0 && Cfg::kPAliasesS) ok = mbar_wait(p_free, (it - 1) & 1, ctx, 23);      // P^T consumed
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue(Cfg::kColS, k_addr, q_addr + qs * Cfg::kTileBytes);
+            umma_commit_pred(leader, s_full);
+            umma_commit_pred(leader, &q_empty[qs]);
+            GQA_TRACE(1, it, 0);
+            ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 24);
+            if (ok && it > 0) ok = mbar_wait(ds_ready, (it - 1) & 1, ctx, 25);                       // dP^T columns read
+            if (ok && it > 0 && Cfg::kDqAliasesDp) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);  // dQ drained
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue(Cfg::kColDP, v_addr, do_addr + dos * Cfg::kTileBytes);
+            umma_commit_pred(leader, dp_full);
+            umma_commit_pred(leader, &do_empty[dos]);
+            GQA_TRACE(1, it, 1);
         }
-    } else if (warp < 4) {
-        // ======================= dQ drain warpgroup =======================
-        const int r = warp * 32 + lane;  // query row inside the tile == TMEM lane
+    } else if (warp == kWarpMmaDV) {
+        // ======================= issuer: dV += P^T dO(it)  (A from TMEM, B = dO read MN-major) =======================
+        const uint32_t leader = elect_one() ? 1u : 0u;
+        const uint32_t idesc = make_idesc_bf16(128, D, false, true);
+        bool ok = true;
+        for (int it = 0; it < n_iter && ok; ++it) {
+            const int dos = it % Cfg::kDOStages;
+            ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 30) && mbar_wait(p_ready, it & 1, ctx, 31);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t b0 = do_addr + dos * Cfg::kTileBytes;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+                umma_ts_pred(leader, tmem + Cfg::kColDV, tmem + p_col_of_kstep<D>(kk),
+                             make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+            umma_commit_pred(leader, p_free);
+            umma_commit_pred(leader, &do_empty[dos]);
+            GQA_TRACE(1, it, 2);
+        }
+        if (ok) umma_commit_pred(leader, acc_full);
+    } else if (warp == kWarpMmaDK) {
+        // ======================= issuer: dK += dS^T Q(it)  (A = dS^T K-major, B = Q read MN-major) =======================
+        const uint32_t leader = elect_one() ? 1u : 0u;
+        const uint32_t idesc = make_idesc_bf16(128, D, false, true);
+        bool ok = true;
+        for (int it = 0; it < n_iter && ok; ++it) {
+            const int qs = it % Cfg::kQStages;
+            ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 32) && mbar_wait(ds_ready, it & 1, ctx, 33);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t b0 = q_addr + qs * Cfg::kTileBytes;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+                umma_ss_pred(leader, tmem + Cfg::kColDK,
+                             make_sdesc_sw128(ds_addr + (kk >> 2) * kPanel + (kk & 3) * 32, 16, 1024),
+                             make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+            umma_commit_pred(leader, ds_free);
+            umma_commit_pred(leader, &q_empty[qs]);
+        }
+        if (ok) umma_commit_pred(leader, acc_full);
+    } else if (warp == kWarpMmaDQ) {
+        // ======================= issuer: dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major) =======================
+        const uint32_t leader = elect_one() ? 1u : 0u;
+        const uint32_t idesc = make_idesc_bf16(128, D, true, true);
+        bool ok = mbar_wait(kv_full, 0, ctx, 34);
+        for (int it = 0; it < n_iter && ok; ++it) {
+            ok = mbar_wait(ds_ready, it & 1, ctx, 35);
+            if (ok && it > 0) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 36);
+            if (!ok) break;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+                umma_ss_pred(leader, tmem + Cfg::kColDQ, make_sdesc_sw128(ds_addr + kk * 2048, kPanel, 1024),
+                             make_sdesc_sw128(k_addr + kk * 2048, kPanel, 1024), idesc, kk > 0);
+            umma_commit_pred(leader, dq_full);
+            umma_commit_pred(leader, ds_free);
+            GQA_TRACE(1, it, 3);
+        }
+    } else if (warp < kWarpEw0) {
+        // ======================= dQ drain warps =======================
+        // Each warp owns 32 query rows: TMEM -> registers -> its own swizzled staging boxes -> TMA reduce-add
+        // into the fp32 accumulator.  The reductions run on the copy engine, off the load/store pipe.
         const uint32_t tDQ = tmem + ((uint32_t)(warp * 32) << 16) + Cfg::kColDQ;
+        uint8_t* stage = sDQ + warp * 8192 + lane * 128;
+        const int sw = lane & 7;
         for (int it = 0; it < n_iter; ++it) {
             if (!mbar_wait(dq_full, it & 1, ctx, 40)) break;
             tc_fence_after_sync();
             GQA_TRACE(2, it, 0);
-            float* dst = p.dq_accum + ((size_t)q_row_of(it) + r) * D;
-            if constexpr (D == 64) {
-                uint32_t v0[32], v1[32];
-                tmem_ld32(tDQ, v0);
-                tmem_ld32(tDQ + 32, v1);
-                tmem_wait_ld();
-                tc_fence_before_sync();
-                mbar_arrive(dq_empty);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * i), "r"(v0[4 * i]),
-                                 "r"(v0[4 * i + 1]), "r"(v0[4 * i + 2]), "r"(v0[4 * i + 3])
-                                 : "memory");
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 32 + 4 * i),
-                                 "r"(v1[4 * i]), "r"(v1[4 * i + 1]), "r"(v1[4 * i + 2]), "r"(v1[4 * i + 3])
-                                 : "memory");
-            } else {
+            const int row = q_row_of(it) + warp * 32;
 #pragma unroll 1
-                for (int ch = 0; ch < D / 32; ++ch) {
+            for (int rnd = 0; rnd < D / 64; ++rnd) {
+#pragma unroll
+                for (int bx = 0; bx < 2; ++bx) {
                     uint32_t v[32];
-                    tmem_ld32(tDQ + ch * 32, v);
+                    tmem_ld32(tDQ + rnd * 64 + bx * 32, v);
                     tmem_wait_ld();
-                    if (ch == D / 32 - 1) {
+                    if (rnd == D / 64 - 1 && bx == 1) {  // every column is in registers: hand the TMEM tile back
                         tc_fence_before_sync();
                         mbar_arrive(dq_empty);
                     }
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + ch * 32 + 4 * i),
-                                     "r"(v[4 * i]), "r"(v[4 * i + 1]), "r"(v[4 * i + 2]), "r"(v[4 * i + 3])
-                                     : "memory");
+                    for (int c8 = 0; c8 < 8; ++c8)
+                        *reinterpret_cast<uint4*>(stage + bx * 4096 + ((c8 ^ sw) << 4)) =
+                            make_uint4(v[4 * c8], v[4 * c8 + 1], v[4 * c8 + 2], v[4 * c8 + 3]);
                 }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_reduce_add_2d(&mapDQ, sDQ + warp * 8192, rnd * 64, row);
+                    tma_reduce_add_2d(&mapDQ, sDQ + warp * 8192 + 4096, rnd * 64 + 32, row);
+                    bulk_commit_group();
+                    bulk_wait_read_all();  // staging boxes may be overwritten after this
+                }
+                __syncwarp();
             }
+            GQA_TRACE(2, it, 1);
         }
-    } else {
+        if (lane == 0) bulk_wait_all();
+    } else if (warp < kWarpTma) {
         // ======================= elementwise warpgroups (P^T and dS^T) =======================
-        const int h = (warp - 4) >> 2;            // which 64 query columns of the tile pair
+        const int w = (warp - kWarpEw0) >> 2;     // which 32 query columns of the tile pair
         const int j = (warp & 3) * 32 + lane;     // key row inside the tile == TMEM lane
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tS = tmem + lane_addr + Cfg::kColS + h * 64;    // this half's S^T columns; P^T goes to the first 32
-        const uint32_t tDP = tmem + lane_addr + Cfg::kColDP + h * 64;
-        uint8_t* ds_row = sDS + h * kPanel + j * 128;
+        const uint32_t tS = tmem + lane_addr + Cfg::kColS + w * 32;
+        const uint32_t tDP = tmem + lane_addr + Cfg::kColDP + w * 32;
+        const uint32_t tP = tmem + lane_addr + (Cfg::kPAliasesS ? (Cfg::kColS + w * 32) : (Cfg::kColP + w * 16));
+        // dS^T row j, query columns [32w, 32w+32): panel w/2, 16-byte chunks (w&1)*4 .. +3
+        uint8_t* ds_row = sDS + (w >> 1) * kPanel + j * 128;
+        const int chunk0 = (w & 1) * 4;
         const float c = p.scale_log2;
+        const bool trace_me = (warp == kWarpEw0);
         bool ok = true;
         for (int it = 0; it < n_iter; ++it) {
             const int qs = it % Cfg::kQStages;
-            const float* lse = sLse + qs * kTile + h * 64;
-            const float* dlt = sDelta + qs * kTile + h * 64;
+            const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + w * 32);
+            const float4* dlt4 = reinterpret_cast<const float4*>(sDelta + qs * kTile + w * 32);
             const bool masked = p.causal && (it % n_qt == 0);  // the diagonal query tile
-            uint32_t pk[32];  // P^T of this thread: 64 query columns, packed bf16 pairs
+            float e[32];  // P^T of this thread (fp32), 32 query columns
             // the Q barrier also carries the LSE and Delta rows of this query tile
-            ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 29) && mbar_wait(s_full, it & 1, ctx, 30);
+            ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 50) && mbar_wait(s_full, it & 1, ctx, 51);
             if (!ok) break;
             tc_fence_after_sync();
-            GQA_TRACE(0, it, 0);
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
+            if (trace_me) GQA_TRACE(0, it, 0);
+            {
                 uint32_t v[32];
-                tmem_ld32(tS + ch * 32, v);
+                tmem_ld32(tS, v);
                 tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int col = ch * 32 + 2 * i;
-                    const float2 l2 = *reinterpret_cast<const float2*>(lse + col);
-                    float e0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), c, -l2.x));
-                    float e1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -l2.y));
-                    if (masked) {  // key j is visible to query i iff j <= i
-                        if (j > h * 64 + col) e0 = 0.f;
-                        if (j > h * 64 + col + 1) e1 = 0.f;
-                    }
-                    pk[ch * 16 + i] = pack_bf16x2(e0, e1);
+                for (int i = 0; i < 8; ++i) {
+                    const float4 l4 = lse4[i];
+                    e[4 * i + 0] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 0]), c, -l4.x));
+                    e[4 * i + 1] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 1]), c, -l4.y));
+                    e[4 * i + 2] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 2]), c, -l4.z));
+                    e[4 * i + 3] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 3]), c, -l4.w));
                 }
-                uint32_t out[16];
+            }
+            if (masked) {  // key j is visible to query i iff j <= i
 #pragma unroll
-                for (int i = 0; i < 16; ++i) out[i] = pk[ch * 16 + i];
-                tmem_st16(tS + ch * 16, out);
+                for (int i = 0; i < 32; ++i)
+                    if (j > w * 32 + i) e[i] = 0.f;
+            }
+            if (!Cfg::kPAliasesS && it > 0) {  // the previous P^T must have been consumed by dV
+                ok = mbar_wait(p_free, (it - 1) & 1, ctx, 52);
+                if (!ok) break;
+                tc_fence_after_sync();
+            }
+            {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(e[2 * i], e[2 * i + 1]);
+                tmem_st16(tP, pk);
             }
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_ready);
-            GQA_TRACE(0, it, 1);
+            if (trace_me) GQA_TRACE(0, it, 1);
 
-            ok = mbar_wait(dp_full, it & 1, ctx, 31);
-            if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 32);
+            ok = mbar_wait(dp_full, it & 1, ctx, 53);
+            if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 54);
             if (!ok) break;
-            GQA_TRACE(0, it, 2);
             tc_fence_after_sync();
+            if (trace_me) GQA_TRACE(0, it, 2);
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t v[32];
-                tmem_ld32(tDP + ch * 32, v);
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t v[16];
+                tmem_ld16(tDP + hf * 16, v);
                 tmem_wait_ld();
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {  // 8 query columns = one 16-byte chunk of the dS^T row
-                    uint32_t w[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int col = ch * 32 + q4 * 8 + 2 * i;
-                        const float2 d2 = *reinterpret_cast<const float2*>(dlt + col);
-                        const uint32_t pp = pk[(col >> 1)];
-                        const float s0 = bf16_lo_to_f32(pp) * (__uint_as_float(v[q4 * 8 + 2 * i]) - d2.x);
-                        const float s1 = bf16_hi_to_f32(pp) * (__uint_as_float(v[q4 * 8 + 2 * i + 1]) - d2.y);
-                        w[i] = pack_bf16x2(s0, s1);
-                    }
-                    const int chunk = ch * 4 + q4;
-                    *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int q2 = 0; q2 < 2; ++q2) {  // 8 query columns = one 16-byte chunk of the dS^T row
+                    const float4 da = dlt4[hf * 4 + q2 * 2], db = dlt4[hf * 4 + q2 * 2 + 1];
+                    const int base = hf * 16 + q2 * 8;
+                    uint4 o;
+                    o.x = pack_bf16x2(e[base + 0] * (__uint_as_float(v[q2 * 8 + 0]) - da.x),
+                                      e[base + 1] * (__uint_as_float(v[q2 * 8 + 1]) - da.y));
+                    o.y = pack_bf16x2(e[base + 2] * (__uint_as_float(v[q2 * 8 + 2]) - da.z),
+                                      e[base + 3] * (__uint_as_float(v[q2 * 8 + 3]) - da.w));
+                    o.z = pack_bf16x2(e[base + 4] * (__uint_as_float(v[q2 * 8 + 4]) - db.x),
+                                      e[base + 5] * (__uint_as_float(v[q2 * 8 + 5]) - db.y));
+                    o.w = pack_bf16x2(e[base + 6] * (__uint_as_float(v[q2 * 8 + 6]) - db.z),
+                                      e[base + 7] * (__uint_as_float(v[q2 * 8 + 7]) - db.w));
+                    const int chunk = chunk0 + hf * 2 + q2;
+                    *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(ds_ready);
-            GQA_TRACE(0, it, 3);
+            if (trace_me) GQA_TRACE(0, it, 3);
         }
-        // ---- epilogue: dV and scale*dK of this key row, half of the columns per warpgroup ----
-        if (ok) ok = mbar_wait(acc_full, 0, ctx, 33);
+        // ---- epilogue: dV and scale*dK of this key row, a quarter of the columns per warpgroup ----
+        if (ok) ok = mbar_wait(acc_full, 0, ctx, 55);
         if (ok) {
             tc_fence_after_sync();
-            constexpr int kHalf = D / 2;
+            constexpr int kQuarter = D / 4;  // 16 or 32 columns
             const size_t grow = (size_t)kv_row0 + j;
 #pragma unroll 1
             for (int which = 0; which < 2; ++which) {
-                const uint32_t tA = tmem + lane_addr + (which == 0 ? Cfg::kColDV : Cfg::kColDK) + h * kHalf;
-                __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + grow * D + h * kHalf;
+                const uint32_t tA = tmem + lane_addr + (which == 0 ? Cfg::kColDV : Cfg::kColDK) + w * kQuarter;
+                __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + grow * D + w * kQuarter;
                 const float mul = which == 0 ? 1.0f : p.scale;
-#pragma unroll 1
-                for (int ch = 0; ch < kHalf / 32; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(tA + ch * 32, v);
+#pragma unroll
+                for (int ch = 0; ch < kQuarter / 16; ++ch) {
+                    uint32_t v[16];
+                    tmem_ld16(tA + ch * 16, v);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                    for (int i = 0; i < 2; ++i) {
                         uint4 o;
                         o.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]) * mul, __uint_as_float(v[8 * i + 1]) * mul);
                         o.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * mul, __uint_as_float(v[8 * i + 3]) * mul);
                         o.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * mul, __uint_as_float(v[8 * i + 5]) * mul);
                         o.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * mul, __uint_as_float(v[8 * i + 7]) * mul);
-                        *reinterpret_cast<uint4*>(dst + ch * 32 + i * 8) = o;
+                        *reinterpret_cast<uint4*>(dst + ch * 16 + i * 8) = o;
                     }
                 }
             }
@@ -456,7 +490,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // ---- teardown ---------------------------------------------------------------
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 13) {
+    if (warp == kWarpMmaS) {
         if (*abort_flag != 0) __nanosleep(20000);  // let in-flight copies and MMAs drain before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
@@ -474,6 +508,9 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     rc = make_panel_tmap(&mv, V, s.kv_rows(), D, kTile);
     if (rc) return rc;
     rc = make_panel_tmap(&mdo, dO, s.q_rows(), D, kTile);
+    if (rc) return rc;
+    CUtensorMap mdq;
+    rc = make_f32_box_tmap(&mdq, dq_accum, s.q_rows(), D, 32);
     if (rc) return rc;
     GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::kSmemTotal));
@@ -493,7 +530,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)(p.n_tiles * s.B * s.Hkv);
-    gqa_bwd_sm100_kernel<D><<<grid, kBwdThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, p);
+    gqa_bwd_sm100_kernel<D><<<grid, kBwdThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, p);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;

@@ -30,6 +30,10 @@ int note_device_timeout(unsigned int word);
 // 128-byte swizzle: one box is a panel of box_rows rows x 128 bytes.
 int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
+// 2-D fp32 tensor map over a row-major [rows, cols] matrix, box = [box_rows, 32 columns] (128 bytes wide),
+// 128-byte swizzle; used for TMA reduce-add of fp32 tiles.
+int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
 // Device word that forward kernels report bounded-wait failures into (per device).
 int forward_status_word(unsigned int** out);
 

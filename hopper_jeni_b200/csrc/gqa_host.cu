@@ -69,6 +69,23 @@ int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
     return GQA_OK;
 }
 
+int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
+        return GQA_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * sizeof(float)};
+    cuuint32_t box[2] = {32u, box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled(f32)");
+    return GQA_OK;
+}
+
 int forward_status_word(unsigned int** out) {
     constexpr int kMaxDev = 64;
     static unsigned int* words[kMaxDev] = {};
