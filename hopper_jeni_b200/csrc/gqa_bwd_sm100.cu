@@ -79,6 +79,9 @@ struct BwdCfg {
     // and dQ reuses the dP^T columns; the p_free / dq_empty barriers guard the reuse.
     static constexpr bool kPAliasesS = (D != 64);
     static constexpr bool kDqAliasesDp = (D != 64);
+    // D = 64: dS^T is also stored as bf16 over the first half of each warpgroup's dP^T columns, so that dK reads
+    // its A operand from TMEM instead of shared memory (shared-memory bandwidth is what bounds this kernel).
+    static constexpr bool kDsInTmem = (D == 64);
     static constexpr uint32_t kColS = 0, kColDP = 128;
     static constexpr uint32_t kColDQ = (D == 64) ? 256 : 128;
     static constexpr uint32_t kColDV = (D == 64) ? 320 : 256;
@@ -260,6 +263,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 24);
             if (ok && it > 0) ok = mbar_wait(ds_ready, (it - 1) & 1, ctx, 25);                       // dP^T columns read
             if (ok && it > 0 && Cfg::kDqAliasesDp) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);  // dQ drained
+            if (ok && it > 0 && Cfg::kDsInTmem) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 27);      // dK read dS^T
             if (!ok) break;
             tc_fence_after_sync();
             issue(Cfg::kColDP, v_addr, do_addr + dos * Cfg::kTileBytes);
@@ -299,10 +303,15 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tc_fence_after_sync();
             const uint32_t b0 = q_addr + qs * Cfg::kTileBytes;
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-                umma_ss_pred(leader, tmem + Cfg::kColDK,
-                             make_sdesc_sw128(ds_addr + (kk >> 2) * kPanel + (kk & 3) * 32, 16, 1024),
-                             make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+            for (int kk = 0; kk < 8; ++kk) {
+                if constexpr (Cfg::kDsInTmem)  // A = bf16 dS^T in the dP^T columns: query columns [16kk, 16kk+16)
+                    umma_ts_pred(leader, tmem + Cfg::kColDK, tmem + Cfg::kColDP + (kk >> 1) * 32 + (kk & 1) * 8,
+                                 make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+                else
+                    umma_ss_pred(leader, tmem + Cfg::kColDK,
+                                 make_sdesc_sw128(ds_addr + (kk >> 2) * kPanel + (kk & 3) * 32, 16, 1024),
+                                 make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+            }
             umma_commit_pred(leader, ds_free);
             umma_commit_pred(leader, &q_empty[qs]);
         }
@@ -368,6 +377,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (lane == 0) bulk_wait_all();
     } else if (warp < kWarpTma) {
         // ======================= elementwise warpgroups (P^T and dS^T) =======================
+        // Rotated by half an iteration: the body of iteration `it` turns dP^T(it) into dS^T(it) and then
+        // S^T(it+1) into P^T(it+1); P^T is carried in registers as packed bf16 (the rounded values the
+        // dV product uses) between the two halves.
         const int w = (warp - kWarpEw0) >> 2;     // which 32 query columns of the tile pair
         const int j = (warp & 3) * 32 + lane;     // key row inside the tile == TMEM lane
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -380,81 +392,124 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         const float c = p.scale_log2;
         const bool trace_me = (warp == kWarpEw0);
         bool ok = true;
-        for (int it = 0; it < n_iter; ++it) {
-            const int qs = it % Cfg::kQStages;
-            const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + w * 32);
-            const float4* dlt4 = reinterpret_cast<const float4*>(sDelta + qs * kTile + w * 32);
-            const bool masked = p.causal && (it % n_qt == 0);  // the diagonal query tile
-            float e[32];  // P^T of this thread (fp32), 32 query columns
-            // the Q barrier also carries the LSE and Delta rows of this query tile
-            ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 50) && mbar_wait(s_full, it & 1, ctx, 51);
-            if (!ok) break;
-            tc_fence_after_sync();
-            if (trace_me) GQA_TRACE(0, it, 0);
-            {
-                uint32_t v[32];
-                tmem_ld32(tS, v);
-                tmem_wait_ld();
+        uint32_t pk_cur[16];  // P^T(it) of this thread: 32 query columns as packed bf16 pairs
+
+        // P^T of 16 columns [16*hf, 16*hf+16) of query tile `itn` from S^T values v -> packed pairs out[0..8)
+        auto p_half = [&](const uint32_t (&v)[16], const float* lse_tile, int hf, bool masked, uint32_t* out) {
+            const float4* l4p = reinterpret_cast<const float4*>(lse_tile + w * 32 + hf * 16);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float4 l4 = lse4[i];
-                    e[4 * i + 0] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 0]), c, -l4.x));
-                    e[4 * i + 1] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 1]), c, -l4.y));
-                    e[4 * i + 2] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 2]), c, -l4.z));
-                    e[4 * i + 3] = ex2_approx(fmaf(__uint_as_float(v[4 * i + 3]), c, -l4.w));
+            for (int i = 0; i < 4; ++i) {
+                const float4 l4 = l4p[i];
+                float e0 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 0]), c, -l4.x));
+                float e1 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 1]), c, -l4.y));
+                float e2 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 2]), c, -l4.z));
+                float e3 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 3]), c, -l4.w));
+                if (masked) {  // key j is visible to query i iff j <= i
+                    const int col = w * 32 + hf * 16 + 4 * i;
+                    if (j > col + 0) e0 = 0.f;
+                    if (j > col + 1) e1 = 0.f;
+                    if (j > col + 2) e2 = 0.f;
+                    if (j > col + 3) e3 = 0.f;
                 }
+                out[2 * i + 0] = pack_bf16x2(e0, e1);
+                out[2 * i + 1] = pack_bf16x2(e2, e3);
             }
-            if (masked) {  // key j is visible to query i iff j <= i
+        };
+        // dS^T of 16 columns from dP^T values v and the packed P^T pairs -> two 16-byte chunks of the dS^T row
+        auto ds_half = [&](const uint32_t (&v)[16], const float* dlt_tile, int hf, const uint32_t* pk, uint32_t* dsp) {
+            const float4* d4p = reinterpret_cast<const float4*>(dlt_tile + w * 32 + hf * 16);
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (j > w * 32 + i) e[i] = 0.f;
+            for (int q2 = 0; q2 < 2; ++q2) {
+                const float4 da = d4p[q2 * 2], db = d4p[q2 * 2 + 1];
+                const uint32_t* pp = pk + q2 * 4;
+                uint4 o;
+                o.x = pack_bf16x2(bf16_lo_to_f32(pp[0]) * (__uint_as_float(v[q2 * 8 + 0]) - da.x),
+                                  bf16_hi_to_f32(pp[0]) * (__uint_as_float(v[q2 * 8 + 1]) - da.y));
+                o.y = pack_bf16x2(bf16_lo_to_f32(pp[1]) * (__uint_as_float(v[q2 * 8 + 2]) - da.z),
+                                  bf16_hi_to_f32(pp[1]) * (__uint_as_float(v[q2 * 8 + 3]) - da.w));
+                o.z = pack_bf16x2(bf16_lo_to_f32(pp[2]) * (__uint_as_float(v[q2 * 8 + 4]) - db.x),
+                                  bf16_hi_to_f32(pp[2]) * (__uint_as_float(v[q2 * 8 + 5]) - db.y));
+                o.w = pack_bf16x2(bf16_lo_to_f32(pp[3]) * (__uint_as_float(v[q2 * 8 + 6]) - db.z),
+                                  bf16_hi_to_f32(pp[3]) * (__uint_as_float(v[q2 * 8 + 7]) - db.w));
+                const int chunk = chunk0 + hf * 2 + q2;
+                *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
+                dsp[q2 * 4 + 0] = o.x;
+                dsp[q2 * 4 + 1] = o.y;
+                dsp[q2 * 4 + 2] = o.z;
+                dsp[q2 * 4 + 3] = o.w;
             }
-            if (!Cfg::kPAliasesS && it > 0) {  // the previous P^T must have been consumed by dV
-                ok = mbar_wait(p_free, (it - 1) & 1, ctx, 52);
-                if (!ok) break;
-                tc_fence_after_sync();
-            }
-            {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(e[2 * i], e[2 * i + 1]);
-                tmem_st16(tP, pk);
-            }
+        };
+        auto publish_p = [&](const uint32_t (&pk)[16]) {
+            tmem_st16(tP, pk);
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_ready);
-            if (trace_me) GQA_TRACE(0, it, 1);
+        };
 
+        // ---- prologue: P^T(0) (the Q barrier also carries the LSE and Delta rows of the query tile)
+        ok = mbar_wait(&q_full[0], 0, ctx, 50) && mbar_wait(s_full, 0, ctx, 51);
+        if (ok) {
+            tc_fence_after_sync();
+            const bool masked0 = p.causal != 0;  // iteration 0 is the diagonal tile when causal
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t v[16];
+                tmem_ld16(tS + hf * 16, v);
+                tmem_wait_ld();
+                p_half(v, sLse, hf, masked0, pk_cur + hf * 8);
+            }
+            publish_p(pk_cur);
+        }
+        for (int it = 0; it < n_iter && ok; ++it) {
+            const int qs = it % Cfg::kQStages, qn = (it + 1) % Cfg::kQStages;
+            const bool more = it + 1 < n_iter;
+            const bool masked_next = p.causal && ((it + 1) % n_qt == 0);
+            const float* dlt_tile = sDelta + qs * kTile;
+            const float* lse_next = sLse + qn * kTile;
+            // ---- dS^T(it) from dP^T(it) and the P^T(it) kept in registers
             ok = mbar_wait(dp_full, it & 1, ctx, 53);
             if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 54);
             if (!ok) break;
             tc_fence_after_sync();
-            if (trace_me) GQA_TRACE(0, it, 2);
+            if (trace_me) GQA_TRACE(0, it, 0);
+            {
+                uint32_t dsp[16];
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                uint32_t v[16];
-                tmem_ld16(tDP + hf * 16, v);
-                tmem_wait_ld();
-#pragma unroll
-                for (int q2 = 0; q2 < 2; ++q2) {  // 8 query columns = one 16-byte chunk of the dS^T row
-                    const float4 da = dlt4[hf * 4 + q2 * 2], db = dlt4[hf * 4 + q2 * 2 + 1];
-                    const int base = hf * 16 + q2 * 8;
-                    uint4 o;
-                    o.x = pack_bf16x2(e[base + 0] * (__uint_as_float(v[q2 * 8 + 0]) - da.x),
-                                      e[base + 1] * (__uint_as_float(v[q2 * 8 + 1]) - da.y));
-                    o.y = pack_bf16x2(e[base + 2] * (__uint_as_float(v[q2 * 8 + 2]) - da.z),
-                                      e[base + 3] * (__uint_as_float(v[q2 * 8 + 3]) - da.w));
-                    o.z = pack_bf16x2(e[base + 4] * (__uint_as_float(v[q2 * 8 + 4]) - db.x),
-                                      e[base + 5] * (__uint_as_float(v[q2 * 8 + 5]) - db.y));
-                    o.w = pack_bf16x2(e[base + 6] * (__uint_as_float(v[q2 * 8 + 6]) - db.z),
-                                      e[base + 7] * (__uint_as_float(v[q2 * 8 + 7]) - db.w));
-                    const int chunk = chunk0 + hf * 2 + q2;
-                    *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
+                for (int hf = 0; hf < 2; ++hf) {
+                    uint32_t vd[16];
+                    tmem_ld16(tDP + hf * 16, vd);
+                    tmem_wait_ld();
+                    ds_half(vd, dlt_tile, hf, pk_cur + hf * 8, dsp + hf * 8);
+                }
+                if constexpr (Cfg::kDsInTmem) {
+                    tmem_st16(tDP, dsp);  // over this thread's own, already consumed, dP^T columns
+                    tmem_wait_st();
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(ds_ready);
+            if (trace_me) GQA_TRACE(0, it, 1);
+            if (!more) break;
+            // ---- P^T(it+1) from S^T(it+1)
+            ok = mbar_wait(&q_full[qn], ((it + 1) / Cfg::kQStages) & 1, ctx, 50) &&
+                 mbar_wait(s_full, (it + 1) & 1, ctx, 51);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (trace_me) GQA_TRACE(0, it, 2);
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t vs[16];
+                tmem_ld16(tS + hf * 16, vs);
+                tmem_wait_ld();
+                p_half(vs, lse_next, hf, masked_next, pk_cur + hf * 8);
+            }
+            if constexpr (!Cfg::kPAliasesS) {
+                ok = mbar_wait(p_free, it & 1, ctx, 52);  // dV(it) has consumed P^T(it): its columns can be rewritten
+                if (!ok) break;
+                tc_fence_after_sync();
+            }
+            publish_p(pk_cur);
             if (trace_me) GQA_TRACE(0, it, 3);
         }
         // ---- epilogue: dV and scale*dK of this key row, a quarter of the columns per warpgroup ----
