@@ -5,9 +5,11 @@
 //   warps 0-3  softmax warpgroup for query tile 0 (thread = query row = TMEM lane)
 //   warps 4-7  softmax warpgroup for query tile 1
 //   warp  8    TMA producer (Q once, K and V rings)
-//   warp  9    UMMA issuer (S = Q K^T into TMEM, O += P V with P read from TMEM)
-// The two query tiles ping-pong: while one warpgroup runs its softmax, the tensor
-// core works on the other tile.  S lives in TMEM (128 fp32 columns per tile), P
+//   warp  9    UMMA issuer for S = Q K^T (both tiles)
+//   warps 10,11 UMMA issuers for O += P V of tile 0 / tile 1 (P read from TMEM)
+// One warp can start a tcgen05.mma only about every 100 cycles whatever its shape, hence three
+// issuers.  The two query tiles ping-pong: while one warpgroup runs its softmax (the exp unit is
+// the bound at D = 64), the tensor core works on the other tile.  S lives in TMEM (128 fp32 columns per tile), P
 // overwrites the first 64 columns of S as packed bf16, O accumulates in TMEM.
 // The running maximum is only refreshed when it grows by more than 2^8, so O is
 // rescaled rarely; the final division by the row sum uses the same maximum.
@@ -23,9 +25,24 @@ namespace {
 
 using namespace sm100;
 
+// Optional timeline tracing (development builds only): block 0 stamps clock64 at a few points per key block.
+#ifdef GQA_FWD_TRACE
+__device__ long long g_fwd_trace[3][64][4];
+#define GQA_FTRACE(role, it, slot)                                                                 \
+    do {                                                                                           \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64 && (threadIdx.x & 31) == 0) \
+            g_fwd_trace[role][it][slot] = clock64();                                               \
+    } while (0)
+#else
+#define GQA_FTRACE(role, it, slot) \
+    do {                           \
+    } while (0)
+#endif
+
 constexpr int kTile = 128;             // query rows per tile and key rows per block
 constexpr int kPanel = kTile * 128;    // bytes of one 64-column panel of a 128-row tile
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;
+constexpr int kWarpTma = 8, kWarpQK = 9, kWarpPV0 = 10;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
@@ -38,7 +55,7 @@ struct FwdCfg {
     static constexpr int kSmemQ = 2 * kTileBytes;
     static constexpr int kSmemKV = 2 * kStages * kTileBytes;
     static constexpr int kBarBytes = 512;
-    static constexpr int kSmemTotal = 1024 + kSmemQ + kSmemKV + kBarBytes;
+    static constexpr int kSmemTotal = kSmemQ + kSmemKV + kBarBytes;  // the dynamic window must start 1024-byte aligned (checked)
     static constexpr uint32_t kTmemCols = 512;
     static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 256 + D;
     static_assert(256 + 2 * D <= 512, "TMEM budget");
@@ -59,8 +76,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const FwdParams p) {
     using Cfg = FwdCfg<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // swizzled panels need 1024-byte alignment; report instead of computing garbage
+        if (threadIdx.x == 0) atomicCAS(p.status, 0u, 0x80000000u | (99u << 20));
+        return;
+    }
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + Cfg::kSmemQ;
     uint8_t* sV = sK + Cfg::kStages * Cfg::kTileBytes;
@@ -69,7 +89,9 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     uint64_t* s_full = bars + 2;                   // [2]
     uint64_t* p_full = bars + 4;                   // [2]
     uint64_t* o_full = bars + 6;                   // [2]
-    uint64_t* k_full = bars + 8;                   // [kStages]
+    uint64_t* pv_done = bars + 8;                  // [2] PV issuer t -> QK issuer: P_t consumed, S_t may be rewritten
+    uint64_t* turn = bars + 10;                    // [2] softmax warpgroup t finished the exp phase of a block
+    uint64_t* k_full = bars + 12;                  // [kStages]
     uint64_t* k_empty = k_full + Cfg::kStages;     // [kStages]
     uint64_t* v_full = k_empty + Cfg::kStages;     // [kStages]
     uint64_t* v_empty = v_full + Cfg::kStages;     // [kStages]
@@ -103,16 +125,18 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
             mbar_init(&o_full[i], 1);
+            mbar_init(&pv_done[i], 1);
+            mbar_init(&turn[i], 128);
         }
         for (int i = 0; i < Cfg::kStages; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
+            mbar_init(&v_empty[i], n_tiles);  // one commit per PV issuer that uses the block
         }
         fence_mbar_init();
     }
-    if (warp == 9) {
+    if (warp == kWarpQK) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -121,7 +145,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 8) {
+    if (warp == kWarpTma) {
         // ======================= TMA producer =======================
         if (elect_one()) {
             tma_prefetch_desc(&mapQ);
@@ -145,74 +169,58 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     tma_load_2d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], pn * 64, kv_row0 + n * kTile);
             }
         }
-    } else if (warp == 9) {
-        // ======================= UMMA issuer =======================
-        if (elect_one()) {
-            const uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
-            const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
-            const uint32_t colS[2] = {Cfg::kColS0, Cfg::kColS1};
-            const uint32_t colO[2] = {Cfg::kColO0, Cfg::kColO1};
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            bool ok = true;
-
-            auto issue_qk = [&](int t, int n) {
-                const int st = n % Cfg::kStages;
+    } else if (warp == kWarpQK) {
+        // ======================= issuer: S_t(n) = Q_t K(n)^T for both tiles =======================
+        // The whole warp runs the loop (uniform control flow); `leader` marks the one lane that issues.
+        const uint32_t leader = elect_one() ? 1u : 0u;
+        const uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
+        const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK);
+        bool ok = true;
+        for (int t = 0; t < n_tiles && ok; ++t) ok = mbar_wait(&q_full[t], 0, ctx, 20);
+        for (int n = 0; n < n_max && ok; ++n) {
+            const int st = n % Cfg::kStages;
+            ok = mbar_wait(&k_full[st], (n / Cfg::kStages) & 1, ctx, 21);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (n >= n_blk[t]) continue;
+                if (n > 0) ok = mbar_wait(&pv_done[t], (n - 1) & 1, ctx, 22);  // P_t(n-1) lives in the S_t columns
+                if (!ok) break;
+                tc_fence_after_sync();
                 const uint32_t a0 = q_addr + t * Cfg::kTileBytes, b0 = k_addr + st * Cfg::kTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kPanel + (kk & 3) * 32;
-                    umma_ss(tmem + colS[t], make_sdesc_sw128(a0 + off, 16, 1024), make_sdesc_sw128(b0 + off, 16, 1024),
-                            idesc_qk, kk > 0);
+                    umma_ss_pred(leader, tmem + (t ? Cfg::kColS1 : Cfg::kColS0), make_sdesc_sw128(a0 + off, 16, 1024),
+                                 make_sdesc_sw128(b0 + off, 16, 1024), idesc_qk, kk > 0);
                 }
-                umma_commit(&s_full[t]);
-            };
-            auto issue_pv = [&](int t, int n) {
+                umma_commit_pred(leader, &s_full[t]);
+                if (t == 0) GQA_FTRACE(1, n, 0);
+            }
+            if (ok) umma_commit_pred(leader, &k_empty[st]);
+        }
+    } else if (warp >= kWarpPV0) {
+        // ======================= issuers: O_t += P_t(n) V(n)  (A = P_t from TMEM, B = V read MN-major) =======================
+        const int t = warp - kWarpPV0;
+        if (t < n_tiles) {
+            const uint32_t leader = elect_one() ? 1u : 0u;
+            const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
+            const uint32_t v_addr = smem_u32(sV);
+            const uint32_t colS = t ? Cfg::kColS1 : Cfg::kColS0, colO = t ? Cfg::kColO1 : Cfg::kColO0;
+            bool ok = true;
+            for (int n = 0; n < n_blk[t] && ok; ++n) {
                 const int st = n % Cfg::kStages;
-                const uint32_t b0 = v_addr + st * Cfg::kTileBytes;
-#pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk) {
-                    umma_ts(tmem + colO[t], tmem + colS[t] + kk * 8, make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024),
-                            idesc_pv, (n > 0 || kk > 0));
-                }
-            };
-
-            // prologue: S_t(0) for both tiles
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                ok = mbar_wait(&q_full[t], 0, ctx, 20);
-                if (ok && t == 0) ok = mbar_wait(&k_full[0], 0, ctx, 21);
+                ok = mbar_wait(&v_full[st], (n / Cfg::kStages) & 1, ctx, 23) && mbar_wait(&p_full[t], n & 1, ctx, 24);
                 if (!ok) break;
                 tc_fence_after_sync();
-                issue_qk(t, 0);
-            }
-            if (ok) umma_commit(&k_empty[0]);
-
-            for (int n = 0; n < n_max && ok; ++n) {
-                const int st = n % Cfg::kStages;
-                bool v_ready = false;
-                // the last tile that still needs block n releases the V stage; same for K of block n+1
-                const int last_user = (n < n_blk[1]) ? 1 : 0;
-                const int last_user_next = (n + 1 < n_blk[1]) ? 1 : 0;
-                for (int t = 0; t < n_tiles && ok; ++t) {
-                    if (n >= n_blk[t]) continue;
-                    ok = mbar_wait(&p_full[t], n & 1, ctx, 22);
-                    if (ok && !v_ready) {
-                        ok = mbar_wait(&v_full[st], (n / Cfg::kStages) & 1, ctx, 23);
-                        v_ready = true;
-                    }
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_pv(t, n);
-                    if (n + 1 == n_blk[t]) umma_commit(&o_full[t]);
-                    if (t == last_user) umma_commit(&v_empty[st]);
-                    if (n + 1 < n_blk[t]) {
-                        const int st1 = (n + 1) % Cfg::kStages;
-                        ok = mbar_wait(&k_full[st1], ((n + 1) / Cfg::kStages) & 1, ctx, 24);
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                        issue_qk(t, n + 1);
-                        if (t == last_user_next) umma_commit(&k_empty[st1]);
-                    }
-                }
+                if (t == 0) GQA_FTRACE(1, n, 1);
+                const uint32_t b0 = v_addr + st * Cfg::kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                    umma_ts_pred(leader, tmem + colO, tmem + colS + kk * 8, make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024),
+                                 idesc_pv, (n > 0 || kk > 0));
+                umma_commit_pred(leader, &pv_done[t]);
+                umma_commit_pred(leader, &v_empty[st]);
+                if (n + 1 == n_blk[t]) umma_commit_pred(leader, &o_full[t]);
+                if (t == 0) GQA_FTRACE(1, n, 2);
             }
         }
     } else {
@@ -233,21 +241,29 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 ok = mbar_wait(&s_full[t], n & 1, ctx, 30);
                 if (!ok) break;
                 tc_fence_after_sync();
+                if (warp == 0) GQA_FTRACE(0, n, 0);
+                if (warp == 4) GQA_FTRACE(2, n, 0);
                 const bool masked = p.causal && (n == diag_block);
-                // pass 1: row maximum
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(tS + ch * 32, v);
-                    tmem_wait_ld();
+                // the whole 128-column row of S into registers (one TMEM round trip), then the row maximum
+                // with four independent partial maxima (a single chain of 128 dependent max ops is slow)
+                uint32_t v[128];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float s = __uint_as_float(v[i]);
-                        const bool dead = masked && (ch * 32 + i > r);
-                        mx = dead ? mx : fmaxf(mx, s);
+                for (int ch = 0; ch < 4; ++ch) tmem_ld32p(tS + ch * 32, v + ch * 32);
+                tmem_wait_ld();
+                float mx;
+                {
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    if (masked) {
+#pragma unroll
+                        for (int i = 0; i < 128; ++i)
+                            m4[i & 3] = (i > r) ? m4[i & 3] : fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 128; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
                     }
+                    mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
                 }
+                if (warp == 0) GQA_FTRACE(0, n, 1);
                 const float m_new = fmaxf(m_run, mx);
                 const bool grow = (m_new - m_run) * c > kRescaleThreshold;  // true on the first block (m_run = -inf)
                 if (__any_sync(0xffffffffu, grow)) {
@@ -267,30 +283,37 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                         }
                     }
                 }
-                // pass 2: P = exp2(c*s - c*m), row sum, packed bf16 back into the S columns
+                // The exp unit is the shared bottleneck.  Warpgroup 1 starts its first exp phase only when
+                // warpgroup 0 has finished its own, which puts the two tiles half a period apart: one tile's
+                // exps then overlap the other tile's tensor-core round trip instead of both idling together.
+                if (t == 1 && n == 0 && n_blk[0] > 0) ok = mbar_wait(&turn[0], 0, ctx, 35);
+                if (!ok) break;
+                // P = exp2(c*s - c*m), row sum (four partial sums), packed bf16 back into the first 64 S columns
                 const float mc = m_run * c;
-#pragma unroll 1
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(tS + ch * 32, v);
-                    tmem_wait_ld();
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        float e0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), c, -mc));
-                        float e1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), c, -mc));
+                        float e0 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i]), c, -mc));
+                        float e1 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i + 1]), c, -mc));
                         if (masked) {
                             if (ch * 32 + 2 * i > r) e0 = 0.f;
                             if (ch * 32 + 2 * i + 1 > r) e1 = 0.f;
                         }
-                        l_run += e0 + e1;
+                        l4[i & 3] += e0 + e1;
                         pk[i] = pack_bf16x2(e0, e1);
                     }
                     tmem_st16(tS + ch * 16, pk);
                 }
+                l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                if (t == 0 && n == 0) mbar_arrive(&turn[0]);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&p_full[t]);
+                if (warp == 0) GQA_FTRACE(0, n, 2);
+                if (warp == 4) GQA_FTRACE(2, n, 2);
             }
             // epilogue: O / l -> bf16, LSE
             if (ok) ok = mbar_wait(&o_full[t], 0, ctx, 31);
@@ -322,7 +345,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // ---- teardown ---------------------------------------------------------------
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kWarpQK) {
         if (*abort_flag != 0) __nanosleep(20000);  // let in-flight copies and MMAs drain before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
@@ -359,6 +382,12 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
 }
 
 }  // namespace
+
+#ifdef GQA_FWD_TRACE
+extern "C" int gqa_debug_copy_fwd_trace(long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, g_fwd_trace, sizeof(g_fwd_trace));
+}
+#endif
 
 int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
                      unsigned int* status, cudaStream_t stream) {

@@ -52,7 +52,42 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// Encoding a tensor map costs several microseconds of host time and the same few (pointer, shape) pairs
+// recur call after call, so the last encodings are kept per host thread.
+struct TmapKey {
+    const void* base;
+    uint64_t rows, cols;
+    uint32_t box_rows, kind;
+    bool operator==(const TmapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && kind == o.kind;
+    }
+};
+struct TmapCache {
+    static constexpr int kSlots = 32;
+    TmapKey keys[kSlots] = {};
+    CUtensorMap maps[kSlots];
+    bool used[kSlots] = {};
+    int next = 0;
+    bool find(const TmapKey& k, CUtensorMap* out) const {
+        for (int i = 0; i < kSlots; ++i)
+            if (used[i] && keys[i] == k) {
+                *out = maps[i];
+                return true;
+            }
+        return false;
+    }
+    void put(const TmapKey& k, const CUtensorMap& m) {
+        keys[next] = k;
+        maps[next] = m;
+        used[next] = true;
+        next = (next + 1) % kSlots;
+    }
+};
+static thread_local TmapCache g_tmaps;
+
 int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    const TmapKey key{base, rows, cols, box_rows, 0u};
+    if (g_tmaps.find(key, out)) return GQA_OK;
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
@@ -66,10 +101,13 @@ int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled");
+    g_tmaps.put(key, *out);
     return GQA_OK;
 }
 
 int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    const TmapKey key{base, rows, cols, box_rows, 1u};
+    if (g_tmaps.find(key, out)) return GQA_OK;
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
@@ -83,6 +121,7 @@ int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled(f32)");
+    g_tmaps.put(key, *out);
     return GQA_OK;
 }
 
