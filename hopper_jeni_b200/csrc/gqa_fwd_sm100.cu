@@ -283,10 +283,20 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                         }
                     }
                 }
-                // The exp unit is the shared bottleneck.  Warpgroup 1 starts its first exp phase only when
-                // warpgroup 0 has finished its own, which puts the two tiles half a period apart: one tile's
-                // exps then overlap the other tile's tensor-core round trip instead of both idling together.
-                if (t == 1 && n == 0 && n_blk[0] > 0) ok = mbar_wait(&turn[0], 0, ctx, 35);
+                // The exp unit is the shared bottleneck, so the two tiles are kept out of phase: one tile's exps
+                // then overlap the other tile's tensor-core round trip instead of both idling together.
+                // D = 128 (tensor and exp work balanced): strict turns 0,1,0,1,... in the exp phase.
+                // D = 64 (exp-bound): only the first exp phase of tile 1 is delayed until tile 0 finished its own;
+                // measured, strict turns cost 5 % there and gain 25 % at D = 128.
+                if constexpr (D == 128) {
+                    if (t == 1) {
+                        if (n < n_blk[0]) ok = mbar_wait(&turn[0], n & 1, ctx, 35);
+                    } else if (n > 0 && n - 1 < n_blk[1]) {
+                        ok = mbar_wait(&turn[1], (n - 1) & 1, ctx, 36);
+                    }
+                } else {
+                    if (t == 1 && n == 0 && n_blk[0] > 0) ok = mbar_wait(&turn[0], 0, ctx, 35);
+                }
                 if (!ok) break;
                 // P = exp2(c*s - c*m), row sum (four partial sums), packed bf16 back into the first 64 S columns
                 const float mc = m_run * c;
@@ -308,7 +318,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     tmem_st16(tS + ch * 16, pk);
                 }
                 l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-                if (t == 0 && n == 0) mbar_arrive(&turn[0]);
+                if (D == 128 || (t == 0 && n == 0)) mbar_arrive(&turn[t]);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&p_full[t]);
