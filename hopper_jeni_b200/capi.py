@@ -36,7 +36,7 @@ EXPORTS = {
     "gqa_launch_count": (ctypes.c_ulonglong, []),
     "gqa_version": (ctypes.c_char_p, []),
     "gqa_selftest_umma": (_i, [_vp, _vp, _fp, _i, _i, _i, _vp]),
-    "gqa_selftest_umma_cycles": (_i, [_vp, _vp, _fp, _i, _i, _i, ctypes.POINTER(ctypes.c_float), _vp]),
+    "gqa_selftest_umma_cycles": (_i, [_vp, _vp, _fp, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_float), _vp]),
     "gqa_checker_fwd_simt": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_checker_bwd_simt": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _fp,
                                   _i, _i, _i, _i, _i, _i, _f, _vp]),

@@ -20,9 +20,10 @@
 //   warps 4-19   four elementwise warpgroups; each owns 32 query columns of the tile pair
 //   warp  20     TMA producer
 //   warps 21-24  UMMA issuers: [S^T, dP^T] | dV | dK | dQ
-// One warp can start a tcgen05.mma only about every 100 cycles whatever its shape, while
-// the tensor pipe needs 32-64 cycles for the products used here, so the five GEMMs are
-// issued by four warps in parallel; mbarriers carry every cross-warp dependency.
+// The five GEMMs wait on different producers, and one issuing warp sustains a 128x64x16 product
+// only every 57 cycles (78 when A comes from TMEM) against 32 cycles of tensor math, so they are
+// issued by four warps in parallel, each a warp-uniform loop with one elected lane; mbarriers
+// carry every cross-warp dependency.
 //
 // Replaces gqa_bwd_vj1d (src/attention/GQA_bwd_baseline.cu:405-547) in the
 // G-loop-inside-the-CTA form of gqa_bwd_vz2_wgmma (src/attention/GQA_bwd.cu:15207-15342);

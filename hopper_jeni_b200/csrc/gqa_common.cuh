@@ -34,6 +34,10 @@ int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
 // 128-byte swizzle; used for TMA reduce-add of fp32 tiles.
 int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
+// 2-D bf16 tensor map over a row-major [rows, 8] matrix (16 bytes per row), box = [box_rows, 8 columns], no swizzle:
+// one box is a "column panel" (rows of 16 bytes) as make_sdesc_noswizzle expects.
+int make_col8_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_rows);
+
 // Device word that forward kernels report bounded-wait failures into (per device).
 int forward_status_word(unsigned int** out);
 

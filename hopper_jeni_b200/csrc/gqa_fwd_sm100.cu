@@ -7,8 +7,8 @@
 //   warp  8    TMA producer (Q once, K and V rings)
 //   warp  9    UMMA issuer for S = Q K^T (both tiles)
 //   warps 10,11 UMMA issuers for O += P V of tile 0 / tile 1 (P read from TMEM)
-// One warp can start a tcgen05.mma only about every 100 cycles whatever its shape, hence three
-// issuers.  The two query tiles ping-pong: while one warpgroup runs its softmax (the exp unit is
+// One issuing warp sustains a product with A in TMEM only every ~78 cycles, and the three GEMM
+// streams wait on different producers, hence three issuers (warp-uniform loops, one elected lane).  The two query tiles ping-pong: while one warpgroup runs its softmax (the exp unit is
 // the bound at D = 64), the tensor core works on the other tile.  S lives in TMEM (128 fp32 columns per tile), P
 // overwrites the first 64 columns of S as packed bf16, O accumulates in TMEM.
 // The running maximum is only refreshed when it grows by more than 2^8, so O is

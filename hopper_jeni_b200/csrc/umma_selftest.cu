@@ -1,7 +1,7 @@
-// Building-block self test: one CTA stages two 128x128 bf16 matrices as
-// 128-byte-swizzled panels (by TMA or by hand), runs a 128 x N x 128 UMMA product
-// in one of six operand arrangements and writes the fp32 result.  It exercises
-// exactly the descriptor helpers the attention kernels use.
+// Building-block self test and issue-rate probe: one CTA stages two 128x128 bf16 matrices as
+// 128-byte-swizzled panels (by TMA or by hand), runs a 128 x N x 128 UMMA product in one of the
+// operand arrangements the attention kernels use and writes the fp32 result.  It exercises exactly
+// the descriptor helpers of sm100_ptx.cuh.
 #include "gqa_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -9,32 +9,51 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kPanelBytes = 128 * 128;  // 128 rows x 128 B
-constexpr int kSmemBytes = 4 * kPanelBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kPanelBytes = 128 * 128;    // 128 rows x 128 B
+constexpr int kColPanelBytes = 128 * 16;  // 128 rows x 16 B (un-swizzled column panel)
+constexpr int kOffBars = 4 * kPanelBytes;
+constexpr int kOffCol = kOffBars + 256;
+constexpr int kSmemBytes = 1024 /*align*/ + kOffCol + 4 * kColPanelBytes;
+
+struct SelftestArgs {
+    const __nv_bfloat16* X;
+    const __nv_bfloat16* Y;
+    float* C;
+    unsigned int* status;
+    long long* cycles;  // null for the correctness run
+    int N, mode, use_tma, reps, two_issuers;
+};
+
+// Descriptor of K step k (16 contraction elements) of a 128x128 operand held as two swizzled panels.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t base, int k, bool mn_major) {
+    return mn_major ? make_sdesc_sw128(base + k * 2048, kPanelBytes, 1024)
+                    : make_sdesc_sw128(base + (k >> 2) * kPanelBytes + (k & 3) * 32, 16, 1024);
+}
 
 __global__ void __launch_bounds__(128, 1)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
-                     const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ Y, float* __restrict__ C,
-                     int N, int mode, int use_tma, unsigned int* status, int reps, long long* cycles, int variant) {
+                     const SelftestArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sX = smem;
     uint8_t* sY = smem + 2 * kPanelBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * kPanelBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
     uint64_t* bar_load = bars + 0;
-    uint64_t* bar_mma = bars + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 3);
+    uint64_t* bar_mma = bars + 1;  // [2]: one per issuing warp
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 4);
+    uint8_t* sCol = smem + kOffCol;  // mode 6: X cols 0-7 | X cols 8-15 | Y cols 0-7 | Y cols 8-15
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
-    AbortCtx ctx{abort_flag, status};
+    const int N = a.N, mode = a.mode;
+    AbortCtx ctx{abort_flag, a.status};
 
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(bar_load, 1);
-        mbar_init(bar_mma, 1);
-        mbar_init(bars + 4, 1);
+        mbar_init(&bar_mma[0], 1);
+        mbar_init(&bar_mma[1], 1);
         fence_mbar_init();
     }
     if (warp == 0) {
@@ -46,8 +65,9 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
+    // ---- stage the operands --------------------------------------------------------------------
     bool ok = true;
-    if (use_tma) {
+    if (a.use_tma) {
         if (tid == 0) {
             mbar_expect_tx(bar_load, 4 * kPanelBytes);
             tma_load_2d(sX, &mapX, bar_load, 0, 0);
@@ -57,20 +77,28 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
         }
         ok = mbar_wait(bar_load, 0, ctx, 1);
     } else {
-        // thread = row; 16 chunks of 16 B per 256-byte row, two panels
-        const uint4* gx = reinterpret_cast<const uint4*>(X + (size_t)tid * 128);
-        const uint4* gy = reinterpret_cast<const uint4*>(Y + (size_t)tid * 128);
+        // thread = row; 16 chunks of 16 B per 256-byte row, two panels, chunk c of row r at c ^ (r & 7)
+        const uint4* gx = reinterpret_cast<const uint4*>(a.X + (size_t)tid * 128);
+        const uint4* gy = reinterpret_cast<const uint4*>(a.Y + (size_t)tid * 128);
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
             const uint32_t off = (c >> 3) * kPanelBytes + tid * 128 + (((c & 7) ^ (tid & 7)) << 4);
             *reinterpret_cast<uint4*>(sX + off) = gx[c];
             *reinterpret_cast<uint4*>(sY + off) = gy[c];
         }
-        fence_proxy_async_smem();
     }
+    if (mode == 6) {  // first 16 columns of X and Y again, as un-swizzled column panels (thread = row)
+        const uint4* gx = reinterpret_cast<const uint4*>(a.X + (size_t)tid * 128);
+        const uint4* gy = reinterpret_cast<const uint4*>(a.Y + (size_t)tid * 128);
+        *reinterpret_cast<uint4*>(sCol + 0 * kColPanelBytes + tid * 16) = gx[0];
+        *reinterpret_cast<uint4*>(sCol + 1 * kColPanelBytes + tid * 16) = gx[1];
+        *reinterpret_cast<uint4*>(sCol + 2 * kColPanelBytes + tid * 16) = gy[0];
+        *reinterpret_cast<uint4*>(sCol + 3 * kColPanelBytes + tid * 16) = gy[1];
+    }
+    fence_proxy_async_smem();
     const uint32_t tmem_a = tmem + 256;  // columns [256,320): bf16 A operand for the TMEM modes
-    if (mode >= 4) {
-        const uint32_t* gx = reinterpret_cast<const uint32_t*>(X + (size_t)tid * 128);
+    if (mode == 4 || mode == 5) {
+        const uint32_t* gx = reinterpret_cast<const uint32_t*>(a.X + (size_t)tid * 128);
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -84,83 +112,74 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
     tc_fence_before_sync();
     __syncthreads();
 
-    if ((warp == 0 || (warp == 1 && (variant & 64))) && ok) {  // a whole warp runs the issue loop; an elected lane issues
+    // ---- issue: the whole warp runs the loop, one elected lane issues ----------------------------
+    if ((warp == 0 || (warp == 1 && a.two_issuers)) && ok) {
         tc_fence_after_sync();
+        const uint32_t leader = elect_one() ? 1u : 0u;
         const bool a_mn = (mode == 2 || mode == 3);
         const bool b_mn = (mode == 1 || mode == 3 || mode == 5);
         const uint32_t idesc = make_idesc_bf16(128, N, a_mn, b_mn);
-        const uint32_t ax = smem_u32(sX), bx = smem_u32(sY);
-        const long long t_issue = clock64();
-        if (variant & 8) {  // lean loop: descriptors precomputed, nothing but the issue in the body
-            uint64_t ad[8], bd[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t off = (N == 256 ? 0 : (k >> 2) * kPanelBytes) + (k & 3) * 32;
-                ad[k] = make_sdesc_sw128(ax + off, 16, 1024);
-                bd[k] = make_sdesc_sw128(bx + off, 16, 1024);
-            }
-            const uint32_t leader = elect_one() ? 1u : 0u;
-            // a second issuing warp (variant bit 6) works on its own accumulator and barrier
-            const uint32_t td = tmem + (warp == 1 ? 128u : 0u);
-            const uint32_t ta = tmem_a;
-#pragma unroll 1
-            for (int rep = 0; rep < reps; ++rep) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if (variant & 16) {
-                        if (mode >= 4) umma_ts_pred(leader, td, ta + k * 8, bd[k], idesc, 1u);
-                        else umma_ss_pred(leader, td, ad[k], bd[k], idesc, 1u);
-                    } else {
-                        if (mode >= 4) umma_ts_warp(td, ta + k * 8, bd[k], idesc, 1u);
-                        else umma_ss_warp(td, ad[k], bd[k], idesc, 1u);
-                    }
-                }
-            }
-        } else
-#pragma unroll 1
-        for (int rep = 0; rep < reps; ++rep)
+        const uint32_t ax = smem_u32(sX), bx = smem_u32(sY), cx = smem_u32(sCol);
+        const uint32_t td = tmem + (warp == 1 ? 128u : 0u);  // a second issuer works on its own accumulator
+        uint64_t ad[8], bd[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint32_t kmaj_off = (k >> 2) * kPanelBytes + (k & 3) * 32;
-            const uint32_t mn_off = k * 2048;
-            const uint64_t bdesc = b_mn ? make_sdesc_sw128(bx + mn_off, kPanelBytes, 1024)
-                                        : make_sdesc_sw128(bx + kmaj_off, 16, 1024);
-            const uint32_t acc = (variant & 2) ? 0u : uint32_t((k > 0) || (rep > 0));
-            const uint32_t d = tmem + ((variant & 1) ? (k & 1) * 64 : 0);
-            if (mode >= 4) {
-                umma_ts_warp(d, tmem_a + k * 8, bdesc, idesc, acc);
-            } else {
-                const uint64_t adesc = a_mn ? make_sdesc_sw128(ax + mn_off, kPanelBytes, 1024)
-                                            : make_sdesc_sw128(ax + kmaj_off, 16, 1024);
-                umma_ss_warp(d, adesc, bdesc, idesc, acc);
+            ad[k] = operand_desc(ax, k, a_mn);
+            bd[k] = operand_desc(bx, k, b_mn);
+        }
+        const long long t_issue = clock64();
+#pragma unroll 1
+        for (int rep = 0; rep < a.reps; ++rep) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t acc = (k > 0 || rep > 0) ? 1u : 0u;
+                if (mode == 4 || mode == 5) umma_ts_pred(leader, td, tmem_a + k * 8, bd[k], idesc, acc);
+                else umma_ss_pred(leader, td, ad[k], bd[k], idesc, acc);
             }
         }
-        uint64_t* done_bar = (warp == 1) ? (bars + 4) : bar_mma;
-        umma_commit_warp(done_bar);
-        if (cycles) {  // throughput probe: time from first issue to completion of the last product
-            mbar_wait(done_bar, 0, ctx, 3);
-            if ((tid & 31) == 0) cycles[warp] = clock64() - t_issue;
+        if (mode == 6)  // once more over columns 0-15, read through the un-swizzled descriptors
+            umma_ss_pred(leader, td, make_sdesc_noswizzle(cx, kColPanelBytes, 128),
+                         make_sdesc_noswizzle(cx + 2 * kColPanelBytes, kColPanelBytes, 128), idesc, 1u);
+        umma_commit_pred(leader, &bar_mma[warp]);
+        if (a.cycles) {  // issue-rate probe: time from first issue to completion of the last product
+            mbar_wait(&bar_mma[warp], 0, ctx, 3);
+            if ((tid & 31) == 0) a.cycles[warp] = clock64() - t_issue;
         }
     }
-    if (warp <= 1) __syncwarp();  // keep lanes 1-31 from spinning on the barrier while lane 0 still issues
-    if (variant & 4) {            // probe variant: nobody polls the barrier while the products run
-        __syncthreads();
-    }
-    if (ok) ok = mbar_wait(bar_mma, 0, ctx, 2);
+    if (warp <= 1) __syncwarp();
+    if (ok) ok = mbar_wait(&bar_mma[0], 0, ctx, 2);
     tc_fence_after_sync();
-    if (ok) {
+    if (ok && !a.cycles) {
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         for (int c = 0; c < N; c += 32) {
             uint32_t r[32];
             tmem_ld32(tmem + lane_base + c, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) C[(size_t)tid * N + c + i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 32; ++i) a.C[(size_t)tid * N + c + i] = __uint_as_float(r[i]);
         }
     }
+    if (a.two_issuers && ok) mbar_wait(&bar_mma[1], 0, ctx, 4);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+int run_selftest(const void* X, const void* Y, float* C, int N, int mode, int use_tma, int reps, int two_issuers,
+                 long long* dcycles, unsigned int* status, cudaStream_t stream) {
+    CUtensorMap mx, my;
+    int rc = gqa::make_panel_tmap(&mx, X, 128, 128, 128);
+    if (rc) return rc;
+    rc = gqa::make_panel_tmap(&my, Y, 128, 128, 128);
+    if (rc) return rc;
+    GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 64, stream));
+    GQA_CUDA_TRY(cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    SelftestArgs a{static_cast<const __nv_bfloat16*>(X), static_cast<const __nv_bfloat16*>(Y), C, status, dcycles,
+                   N, mode, use_tma, reps, two_issuers};
+    umma_selftest_kernel<<<1, 128, kSmemBytes, stream>>>(mx, my, a);
+    gqa::count_launch();
+    GQA_CUDA_TRY(cudaGetLastError());
+    return GQA_OK;
 }
 
 }  // namespace
@@ -169,52 +188,30 @@ extern "C" int gqa_selftest_umma(const void* X, const void* Y, float* C, int N, 
                                  gqa_stream_t stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     if (!X || !Y || !C) return GQA_ERR_BAD_ARGUMENT;
-    if ((N != 64 && N != 128) || mode < 0 || mode > 5) return GQA_ERR_UNSUPPORTED;
+    if ((N != 64 && N != 128) || mode < 0 || mode > 6) return GQA_ERR_UNSUPPORTED;
     if (!gqa::aligned16(X) || !gqa::aligned16(Y) || !gqa::aligned16(C)) return GQA_ERR_BAD_ARGUMENT;
-    CUtensorMap mx, my;
-    int rc = gqa::make_panel_tmap(&mx, X, 128, 128, 128);
-    if (rc) return rc;
-    rc = gqa::make_panel_tmap(&my, Y, 128, 128, 128);
-    if (rc) return rc;
     unsigned int* status = nullptr;
-    rc = gqa::forward_status_word(&status);
+    int rc = gqa::forward_status_word(&status);
     if (rc) return rc;
-    GQA_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(unsigned int), stream));
-    GQA_CUDA_TRY(cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    umma_selftest_kernel<<<1, 128, kSmemBytes, stream>>>(mx, my, static_cast<const __nv_bfloat16*>(X),
-                                                         static_cast<const __nv_bfloat16*>(Y), C, N, mode, use_tma,
-                                                         status, 1, nullptr, 0);
-    gqa::count_launch();
-    GQA_CUDA_TRY(cudaGetLastError());
+    rc = run_selftest(X, Y, C, N, mode, use_tma, 1, 0, nullptr, status, stream);
+    if (rc) return rc;
     return gqa_check_status(nullptr, stream_);
 }
 
-// Throughput probe for the same six operand arrangements: `reps` x 8 back-to-back K = 16 products
-// accumulating into one TMEM tile; reports the average tensor-pipe cycles per product.  Values of C
-// are meaningless for reps > 1 (the sum is repeated).  Synchronises `stream`.
+// Issue-rate probe for arrangements 0-5: `reps` x 8 back-to-back K = 16 products accumulating into one
+// TMEM tile, issued by one warp (two_issuers = 0) or by two warps on separate accumulators; reports the
+// SM cycles per product per issuing warp.  Synchronises `stream`.
 extern "C" int gqa_selftest_umma_cycles(const void* X, const void* Y, float* C, int N, int mode, int reps,
-                                        float* cycles_per_product, gqa_stream_t stream_) {
-    const int variant = mode >> 8;  // development knobs in the high bits (0 = the documented behaviour)
-    mode &= 0xff;
+                                        int two_issuers, float* cycles_per_product, gqa_stream_t stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     if (!X || !Y || !C || !cycles_per_product || reps < 1) return GQA_ERR_BAD_ARGUMENT;
-    if ((N != 64 && N != 128 && !(variant && N == 256)) || mode < 0 || mode > 5) return GQA_ERR_UNSUPPORTED;
-    CUtensorMap mx, my;
-    int rc = gqa::make_panel_tmap(&mx, X, 128, 128, 128);
-    if (rc) return rc;
-    rc = gqa::make_panel_tmap(&my, Y, 128, 128, 128);
-    if (rc) return rc;
+    if ((N != 64 && N != 128) || mode < 0 || mode > 5) return GQA_ERR_UNSUPPORTED;
     unsigned int* status = nullptr;
-    rc = gqa::forward_status_word(&status);
+    int rc = gqa::forward_status_word(&status);
     if (rc) return rc;
     long long* dcycles = reinterpret_cast<long long*>(status + 2);  // the status allocation is 256 bytes
-    GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 64, stream));
-    GQA_CUDA_TRY(cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    umma_selftest_kernel<<<1, 128, kSmemBytes, stream>>>(mx, my, static_cast<const __nv_bfloat16*>(X),
-                                                         static_cast<const __nv_bfloat16*>(Y), C, N, mode, 1, status,
-                                                         reps, dcycles, variant);
-    gqa::count_launch();
-    GQA_CUDA_TRY(cudaGetLastError());
+    rc = run_selftest(X, Y, C, N, mode, 1, reps, two_issuers ? 1 : 0, dcycles, status, stream);
+    if (rc) return rc;
     long long h[2] = {0, 0};
     GQA_CUDA_TRY(cudaMemcpyAsync(h, dcycles, sizeof h, cudaMemcpyDeviceToHost, stream));
     GQA_CUDA_TRY(cudaStreamSynchronize(stream));

@@ -157,6 +157,8 @@ const char* gqa_version(void);
  *   mode 3: C = X^T * Y    (A MN-major, B MN-major)
  *   mode 4: C = X  * Y^T   (A from tensor memory, B K-major)
  *   mode 5: C = X  * Y     (A from tensor memory, B MN-major)
+ *   mode 6: C = X  * Y^T + X[:, :16] * Y[:, :16]^T  (mode 0 plus one K step read through
+ *           un-swizzled 16-byte-row column panels)
  * N is 64 or 128 (for N = 64 only the first 64 rows/columns of Y are used).
  * use_tma != 0 stages X and Y with TMA tile loads, otherwise threads write the
  * swizzled layout themselves.  Synchronises `stream`.  No counterpart in the
@@ -166,12 +168,13 @@ int gqa_selftest_umma(const void* X, const void* Y, float* C, int N, int mode, i
                       gqa_stream_t stream);
 
 /*
- * Throughput probe over the same arrangements: reps x 8 back-to-back K = 16 products into one
- * accumulator; *cycles_per_product receives the average SM cycles per product (host memory).
+ * Issue-rate probe over arrangements 0-5: reps x 8 back-to-back K = 16 products into one
+ * accumulator, issued by one warp or (two_issuers != 0) by two warps on separate accumulators;
+ * *cycles_per_product (host memory) receives the SM cycles per product per issuing warp.
  * C is scratch.  Synchronises `stream`.  No counterpart in the reference.
  */
 int gqa_selftest_umma_cycles(const void* X, const void* Y, float* C, int N, int mode, int reps,
-                             float* cycles_per_product, gqa_stream_t stream);
+                             int two_issuers, float* cycles_per_product, gqa_stream_t stream);
 
 /*
  * CUDA-core checker kernels (diagnostics): a slow, simple restatement of forward
