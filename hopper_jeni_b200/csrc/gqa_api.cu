@@ -86,16 +86,17 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
     if (rc) return rc;
     char* w = static_cast<char*>(workspace);
     unsigned int* status = reinterpret_cast<unsigned int*>(w + ws.status_off);
-    float* delta = reinterpret_cast<float*>(w + ws.delta_off);
-    float* lse2 = reinterpret_cast<float*>(w + ws.lse2_off);
+    void* lse_cols = w + ws.lse_cols_off;
+    void* delta_cols = w + ws.delta_cols_off;
     float* dq_accum = reinterpret_cast<float*>(w + ws.dq_accum_off);
 
     GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, stream));
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[0], stream));
-    rc = gqa::launch_bwd_preprocess(O, dO, LSE, delta, lse2, dq_accum, s.q_rows(), D, stream);
+    rc = gqa::launch_bwd_preprocess(O, dO, LSE, 1.0f / scale, nullptr, lse_cols, delta_cols, dq_accum, s.q_rows(), D,
+                                    stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[1], stream));
-    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse2, delta, dq_accum, dK, dV, s, status, stream);
+    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dK, dV, s, status, stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[2], stream));
     rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream);
@@ -216,7 +217,8 @@ extern "C" int gqa_checker_bwd_simt(const void* Q, const void* K, const void* V,
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || (D != 64 && D != 128) || Hq % Hkv) return GQA_ERR_UNSUPPORTED;
     const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    int rc = gqa::launch_bwd_preprocess(O, dO, nullptr, delta_scratch, nullptr, nullptr, s.q_rows(), D, stream);
+    int rc = gqa::launch_bwd_preprocess(O, dO, nullptr, 0.f, delta_scratch, nullptr, nullptr, nullptr, s.q_rows(), D,
+                                        stream);
     if (rc) return rc;
     return gqa::launch_bwd_simt(Q, K, V, dO, LSE, delta_scratch, dQ, dK, dV, s, stream);
 }

@@ -9,8 +9,12 @@
 //
 // Everything is computed in the transposed orientation so that a TMEM lane is a
 // key row:  S^T = K Q^T,  dP^T = V dO^T  (both operands K-major from TMA panels),
-//   P^T  = exp2(S^T * scale*log2e - LSE*log2e)   -> bf16 into TMEM (A operand of dV)
+//   P^T  = exp2(scale*log2e * (S^T - LSE/scale))  -> bf16 into TMEM (A operand of dV)
 //   dS^T = P^T * (dP^T - Delta)                   -> bf16 into swizzled shared memory
+// The two subtractions are done by the tensor core: -LSE/scale and -Delta of every query row are split
+// into three bf16 terms by the preprocess kernel and enter S^T and dP^T as one extra K step against a
+// constant "ones" operand.  That removes the per-element broadcast loads of LSE and Delta from shared
+// memory, whose bandwidth is what bounds this kernel.
 //   dV  += P^T dO      (A from TMEM,  B = dO panel read MN-major)
 //   dK  += dS^T Q      (A = dS^T K-major, B = Q panel read MN-major)
 //   dQ   = dS K        (A = dS^T read MN-major, B = K panel read MN-major)
@@ -64,16 +68,19 @@ struct BwdCfg {
     static constexpr int kTileBytes = kPanels * kPanel;
     static constexpr int kQStages = 2;
     static constexpr int kDOStages = (D == 64) ? 2 : 1;
-    static constexpr int kVecBytes = kTile * 4;  // 128 floats of LSE*log2e or Delta
+    static constexpr int kColPanel = kTile * 16;  // 128 rows x 16 B: an un-swizzled 8-column operand panel
+    static constexpr int kDqBoxes = (D == 64) ? 2 : 1;  // 32-column fp32 boxes staged per drain round and warp
     static constexpr int kOffK = 0;
     static constexpr int kOffV = kOffK + kTileBytes;
     static constexpr int kOffQ = kOffV + kTileBytes;
     static constexpr int kOffDO = kOffQ + kQStages * kTileBytes;
     static constexpr int kOffDS = kOffDO + kDOStages * kTileBytes;
-    static constexpr int kOffDQ = kOffDS + 2 * kPanel;   // dQ staging: 4 drain warps x 2 boxes x (32 rows x 128 B)
-    static constexpr int kOffLse = kOffDQ + 4 * 2 * 4096;
-    static constexpr int kOffDelta = kOffLse + kQStages * kVecBytes;
-    static constexpr int kOffBars = kOffDelta + kQStages * kVecBytes;
+    static constexpr int kOffDQ = kOffDS + 2 * kPanel;   // dQ staging: 4 drain warps x kDqBoxes x (32 rows x 128 B)
+    static constexpr int kOffOnes = kOffDQ + 4 * kDqBoxes * 4096;   // constant A operand of the extra K step
+    static constexpr int kOffLseCol = kOffOnes + kColPanel;         // [kQStages] -LSE/scale columns of the query tile
+    static constexpr int kOffDltCol = kOffLseCol + kQStages * kColPanel;  // [kDOStages] -Delta columns
+    static constexpr int kOffZero = kOffDltCol + kDOStages * kColPanel;   // all-zero panel (columns 8-15 of every one)
+    static constexpr int kOffBars = kOffZero + kColPanel;
     static constexpr int kSmemTotal = kOffBars + 256;  // the dynamic window must start 1024-byte aligned (checked)
     static constexpr uint32_t kTmemCols = 512;
     // fp32 column map.  D = 64: every tile has its own columns.  D = 128: P^T overwrites the S^T columns
@@ -94,8 +101,6 @@ struct BwdCfg {
 };
 
 struct BwdParams {
-    const float* lse2;   // [B*Hq*S] LSE * log2(e)
-    const float* delta;  // [B*Hq*S]
     float* dq_accum;     // [B*Hq*S, D] fp32, zeroed by the preprocess stage
     __nv_bfloat16* dK;
     __nv_bfloat16* dV;
@@ -116,7 +121,8 @@ template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
-                     const __grid_constant__ CUtensorMap mapDQ, const BwdParams p) {
+                     const __grid_constant__ CUtensorMap mapDQ, const __grid_constant__ CUtensorMap mapLseCol,
+                     const __grid_constant__ CUtensorMap mapDltCol, const BwdParams p) {
     using Cfg = BwdCfg<D>;
     extern __shared__ __align__(1024) uint8_t smem[];
     if ((smem_u32(smem) & 1023u) != 0) {  // swizzled panels need 1024-byte alignment; report instead of computing garbage
@@ -129,8 +135,10 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     uint8_t* sDO = smem + Cfg::kOffDO;
     uint8_t* sDS = smem + Cfg::kOffDS;
     uint8_t* sDQ = smem + Cfg::kOffDQ;
-    float* sLse = reinterpret_cast<float*>(smem + Cfg::kOffLse);
-    float* sDelta = reinterpret_cast<float*>(smem + Cfg::kOffDelta);
+    uint8_t* sOnes = smem + Cfg::kOffOnes;
+    uint8_t* sLseCol = smem + Cfg::kOffLseCol;
+    uint8_t* sDltCol = smem + Cfg::kOffDltCol;
+    uint8_t* sZero = smem + Cfg::kOffZero;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
     uint64_t* kv_full = bars + 0;    // TMA: K and V tiles
     uint64_t* s_full = bars + 1;     // issuer S   -> elementwise: S^T(it) complete
@@ -195,6 +203,11 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
+    if (tid < kTile) {  // constant operands: ones in columns 0-2 (one per bf16 term of the split), zeros elsewhere
+        *reinterpret_cast<uint4*>(sOnes + tid * 16) = make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u);
+        *reinterpret_cast<uint4*>(sZero + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
+        fence_proxy_async_smem();
+    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -210,6 +223,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tma_prefetch_desc(&mapV);
             tma_prefetch_desc(&mapDO);
             tma_prefetch_desc(&mapDQ);
+            tma_prefetch_desc(&mapLseCol);
+            tma_prefetch_desc(&mapDltCol);
             mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
             for (int pn = 0; pn < Cfg::kPanels; ++pn) {
                 tma_load_2d(sK + pn * kPanel, &mapK, kv_full, pn * 64, kv_row0);
@@ -221,21 +236,21 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     const int st = it % Cfg::kQStages;
                     const uint32_t use = it / Cfg::kQStages;
                     if (use > 0 && !mbar_wait(&q_empty[st], (use - 1) & 1, ctx, 10)) break;
-                    // LSE and Delta ride with Q: their buffers are released with the Q stage, i.e. only
-                    // after the elementwise warpgroups have finished the iteration that reads them
-                    mbar_expect_tx(&q_full[st], Cfg::kTileBytes + 2 * Cfg::kVecBytes);
+                    // the -LSE/scale columns of the tile ride with Q (both are operands of S^T)
+                    mbar_expect_tx(&q_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
                         tma_load_2d(sQ + st * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[st], pn * 64, row);
-                    bulk_load_1d(sLse + st * kTile, p.lse2 + row, Cfg::kVecBytes, &q_full[st]);
-                    bulk_load_1d(sDelta + st * kTile, p.delta + row, Cfg::kVecBytes, &q_full[st]);
+                    tma_load_2d(sLseCol + st * Cfg::kColPanel, &mapLseCol, &q_full[st], 0, row);
                 }
                 {
                     const int st = it % Cfg::kDOStages;
                     const uint32_t use = it / Cfg::kDOStages;
                     if (use > 0 && !mbar_wait(&do_empty[st], (use - 1) & 1, ctx, 11)) break;
-                    mbar_expect_tx(&do_full[st], Cfg::kTileBytes);
+                    // the -Delta columns ride with dO (both are operands of dP^T)
+                    mbar_expect_tx(&do_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
                         tma_load_2d(sDO + st * Cfg::kTileBytes + pn * kPanel, &mapDO, &do_full[st], pn * 64, row);
+                    tma_load_2d(sDltCol + st * Cfg::kColPanel, &mapDltCol, &do_full[st], 0, row);
                 }
             }
         }
@@ -244,13 +259,19 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // The whole warp runs the loop (uniform control flow); `leader` marks the one lane that issues.
         const uint32_t leader = elect_one() ? 1u : 0u;
         const uint32_t idesc = make_idesc_bf16(128, 128, false, false);
-        auto issue = [&](uint32_t col, uint32_t a0, uint32_t b0) {
+        // A operand of the extra K step: ones in columns 0-2 (un-swizzled column panel), columns 8-15 = the zero panel
+        const uint32_t ones_addr = smem_u32(sOnes), zero_addr = smem_u32(sZero);
+        const uint64_t ones_desc = make_sdesc_noswizzle(ones_addr, zero_addr - ones_addr, 128);
+        auto issue = [&](uint32_t col, uint32_t a0, uint32_t b0, uint32_t cols_addr) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
                 const uint32_t off = (kk >> 2) * kPanel + (kk & 3) * 32;
                 umma_ss_pred(leader, tmem + col, make_sdesc_sw128(a0 + off, 16, 1024),
                              make_sdesc_sw128(b0 + off, 16, 1024), idesc, kk > 0);
             }
+            // + 1 * (hi + mid + lo) of the per-query-row term (-LSE/scale or -Delta)
+            umma_ss_pred(leader, tmem + col, ones_desc, make_sdesc_noswizzle(cols_addr, zero_addr - cols_addr, 128), idesc,
+                         1u);
         };
         bool ok = mbar_wait(kv_full, 0, ctx, 20);
         for (int it = 0; it < n_iter && ok; ++it) {
@@ -260,7 +281,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             if (ok && it > 0 && Cfg::kPAliasesS) ok = mbar_wait(p_free, (it - 1) & 1, ctx, 23);      // P^T consumed
             if (!ok) break;
             tc_fence_after_sync();
-            issue(Cfg::kColS, k_addr, q_addr + qs * Cfg::kTileBytes);
+            issue(Cfg::kColS, k_addr, q_addr + qs * Cfg::kTileBytes, smem_u32(sLseCol) + qs * Cfg::kColPanel);
             umma_commit_pred(leader, s_full);
             umma_commit_pred(leader, &q_empty[qs]);
             GQA_TRACE(1, it, 0);
@@ -270,7 +291,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             if (ok && it > 0 && Cfg::kDsInTmem) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 27);      // dK read dS^T
             if (!ok) break;
             tc_fence_after_sync();
-            issue(Cfg::kColDP, v_addr, do_addr + dos * Cfg::kTileBytes);
+            issue(Cfg::kColDP, v_addr, do_addr + dos * Cfg::kTileBytes, smem_u32(sDltCol) + dos * Cfg::kColPanel);
             umma_commit_pred(leader, dp_full);
             umma_commit_pred(leader, &do_empty[dos]);
             GQA_TRACE(1, it, 1);
@@ -343,21 +364,23 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // Each warp owns 32 query rows: TMEM -> registers -> its own swizzled staging boxes -> TMA reduce-add
         // into the fp32 accumulator.  The reductions run on the copy engine, off the load/store pipe.
         const uint32_t tDQ = tmem + ((uint32_t)(warp * 32) << 16) + Cfg::kColDQ;
-        uint8_t* stage = sDQ + warp * 8192 + lane * 128;
+        constexpr int kWarpStage = Cfg::kDqBoxes * 4096;
+        uint8_t* stage = sDQ + warp * kWarpStage + lane * 128;
         const int sw = lane & 7;
         for (int it = 0; it < n_iter; ++it) {
             if (!mbar_wait(dq_full, it & 1, ctx, 40)) break;
             tc_fence_after_sync();
             GQA_TRACE(2, it, 0);
             const int row = q_row_of(it) + warp * 32;
+            constexpr int kRounds = D / (32 * Cfg::kDqBoxes);
 #pragma unroll 1
-            for (int rnd = 0; rnd < D / 64; ++rnd) {
+            for (int rnd = 0; rnd < kRounds; ++rnd) {
 #pragma unroll
-                for (int bx = 0; bx < 2; ++bx) {
+                for (int bx = 0; bx < Cfg::kDqBoxes; ++bx) {
                     uint32_t v[32];
-                    tmem_ld32(tDQ + rnd * 64 + bx * 32, v);
+                    tmem_ld32(tDQ + (rnd * Cfg::kDqBoxes + bx) * 32, v);
                     tmem_wait_ld();
-                    if (rnd == D / 64 - 1 && bx == 1) {  // every column is in registers: hand the TMEM tile back
+                    if (rnd == kRounds - 1 && bx == Cfg::kDqBoxes - 1) {  // every column is in registers: hand the TMEM tile back
                         tc_fence_before_sync();
                         mbar_arrive(dq_empty);
                     }
@@ -369,8 +392,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_reduce_add_2d(&mapDQ, sDQ + warp * 8192, rnd * 64, row);
-                    tma_reduce_add_2d(&mapDQ, sDQ + warp * 8192 + 4096, rnd * 64 + 32, row);
+#pragma unroll
+                    for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)
+                        tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage + bx * 4096, (rnd * Cfg::kDqBoxes + bx) * 32, row);
                     bulk_commit_group();
                     bulk_wait_read_all();  // staging boxes may be overwritten after this
                 }
@@ -398,16 +422,14 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         bool ok = true;
         uint32_t pk_cur[16];  // P^T(it) of this thread: 32 query columns as packed bf16 pairs
 
-        // P^T of 16 columns [16*hf, 16*hf+16) of query tile `itn` from S^T values v -> packed pairs out[0..8)
-        auto p_half = [&](const uint32_t (&v)[16], const float* lse_tile, int hf, bool masked, uint32_t* out) {
-            const float4* l4p = reinterpret_cast<const float4*>(lse_tile + w * 32 + hf * 16);
+        // P^T of 16 columns [16*hf, 16*hf+16) from the S^T values v (which already hold S - LSE/scale) -> packed pairs
+        auto p_half = [&](const uint32_t (&v)[16], int hf, bool masked, uint32_t* out) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float4 l4 = l4p[i];
-                float e0 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 0]), c, -l4.x));
-                float e1 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 1]), c, -l4.y));
-                float e2 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 2]), c, -l4.z));
-                float e3 = ex2_approx(fmaf(__uint_as_float(v[4 * i + 3]), c, -l4.w));
+                float e0 = ex2_approx(__uint_as_float(v[4 * i + 0]) * c);
+                float e1 = ex2_approx(__uint_as_float(v[4 * i + 1]) * c);
+                float e2 = ex2_approx(__uint_as_float(v[4 * i + 2]) * c);
+                float e3 = ex2_approx(__uint_as_float(v[4 * i + 3]) * c);
                 if (masked) {  // key j is visible to query i iff j <= i
                     const int col = w * 32 + hf * 16 + 4 * i;
                     if (j > col + 0) e0 = 0.f;
@@ -419,22 +441,21 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 out[2 * i + 1] = pack_bf16x2(e2, e3);
             }
         };
-        // dS^T of 16 columns from dP^T values v and the packed P^T pairs -> two 16-byte chunks of the dS^T row
-        auto ds_half = [&](const uint32_t (&v)[16], const float* dlt_tile, int hf, const uint32_t* pk, uint32_t* dsp) {
-            const float4* d4p = reinterpret_cast<const float4*>(dlt_tile + w * 32 + hf * 16);
+        // dS^T of 16 columns from the dP^T values v (which already hold dP - Delta) and the packed P^T pairs
+        // -> two 16-byte chunks of the dS^T row (and the same packed values for the TMEM copy)
+        auto ds_half = [&](const uint32_t (&v)[16], int hf, const uint32_t* pk, uint32_t* dsp) {
 #pragma unroll
             for (int q2 = 0; q2 < 2; ++q2) {
-                const float4 da = d4p[q2 * 2], db = d4p[q2 * 2 + 1];
                 const uint32_t* pp = pk + q2 * 4;
                 uint4 o;
-                o.x = pack_bf16x2(bf16_lo_to_f32(pp[0]) * (__uint_as_float(v[q2 * 8 + 0]) - da.x),
-                                  bf16_hi_to_f32(pp[0]) * (__uint_as_float(v[q2 * 8 + 1]) - da.y));
-                o.y = pack_bf16x2(bf16_lo_to_f32(pp[1]) * (__uint_as_float(v[q2 * 8 + 2]) - da.z),
-                                  bf16_hi_to_f32(pp[1]) * (__uint_as_float(v[q2 * 8 + 3]) - da.w));
-                o.z = pack_bf16x2(bf16_lo_to_f32(pp[2]) * (__uint_as_float(v[q2 * 8 + 4]) - db.x),
-                                  bf16_hi_to_f32(pp[2]) * (__uint_as_float(v[q2 * 8 + 5]) - db.y));
-                o.w = pack_bf16x2(bf16_lo_to_f32(pp[3]) * (__uint_as_float(v[q2 * 8 + 6]) - db.z),
-                                  bf16_hi_to_f32(pp[3]) * (__uint_as_float(v[q2 * 8 + 7]) - db.w));
+                o.x = pack_bf16x2(bf16_lo_to_f32(pp[0]) * __uint_as_float(v[q2 * 8 + 0]),
+                                  bf16_hi_to_f32(pp[0]) * __uint_as_float(v[q2 * 8 + 1]));
+                o.y = pack_bf16x2(bf16_lo_to_f32(pp[1]) * __uint_as_float(v[q2 * 8 + 2]),
+                                  bf16_hi_to_f32(pp[1]) * __uint_as_float(v[q2 * 8 + 3]));
+                o.z = pack_bf16x2(bf16_lo_to_f32(pp[2]) * __uint_as_float(v[q2 * 8 + 4]),
+                                  bf16_hi_to_f32(pp[2]) * __uint_as_float(v[q2 * 8 + 5]));
+                o.w = pack_bf16x2(bf16_lo_to_f32(pp[3]) * __uint_as_float(v[q2 * 8 + 6]),
+                                  bf16_hi_to_f32(pp[3]) * __uint_as_float(v[q2 * 8 + 7]));
                 const int chunk = chunk0 + hf * 2 + q2;
                 *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
                 dsp[q2 * 4 + 0] = o.x;
@@ -450,8 +471,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             mbar_arrive(p_ready);
         };
 
-        // ---- prologue: P^T(0) (the Q barrier also carries the LSE and Delta rows of the query tile)
-        ok = mbar_wait(&q_full[0], 0, ctx, 50) && mbar_wait(s_full, 0, ctx, 51);
+        // ---- prologue: P^T(0)
+        ok = mbar_wait(s_full, 0, ctx, 51);
         if (ok) {
             tc_fence_after_sync();
             const bool masked0 = p.causal != 0;  // iteration 0 is the diagonal tile when causal
@@ -460,16 +481,13 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 uint32_t v[16];
                 tmem_ld16(tS + hf * 16, v);
                 tmem_wait_ld();
-                p_half(v, sLse, hf, masked0, pk_cur + hf * 8);
+                p_half(v, hf, masked0, pk_cur + hf * 8);
             }
             publish_p(pk_cur);
         }
         for (int it = 0; it < n_iter && ok; ++it) {
-            const int qs = it % Cfg::kQStages, qn = (it + 1) % Cfg::kQStages;
             const bool more = it + 1 < n_iter;
             const bool masked_next = p.causal && ((it + 1) % n_qt == 0);
-            const float* dlt_tile = sDelta + qs * kTile;
-            const float* lse_next = sLse + qn * kTile;
             // ---- dS^T(it) from dP^T(it) and the P^T(it) kept in registers
             ok = mbar_wait(dp_full, it & 1, ctx, 53);
             if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 54);
@@ -483,7 +501,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     uint32_t vd[16];
                     tmem_ld16(tDP + hf * 16, vd);
                     tmem_wait_ld();
-                    ds_half(vd, dlt_tile, hf, pk_cur + hf * 8, dsp + hf * 8);
+                    ds_half(vd, hf, pk_cur + hf * 8, dsp + hf * 8);
                 }
                 if constexpr (Cfg::kDsInTmem) {
                     tmem_st16(tDP, dsp);  // over this thread's own, already consumed, dP^T columns
@@ -496,8 +514,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             if (trace_me) GQA_TRACE(0, it, 1);
             if (!more) break;
             // ---- P^T(it+1) from S^T(it+1)
-            ok = mbar_wait(&q_full[qn], ((it + 1) / Cfg::kQStages) & 1, ctx, 50) &&
-                 mbar_wait(s_full, (it + 1) & 1, ctx, 51);
+            ok = mbar_wait(s_full, (it + 1) & 1, ctx, 51);
             if (!ok) break;
             tc_fence_after_sync();
             if (trace_me) GQA_TRACE(0, it, 2);
@@ -506,7 +523,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 uint32_t vs[16];
                 tmem_ld16(tS + hf * 16, vs);
                 tmem_wait_ld();
-                p_half(vs, lse_next, hf, masked_next, pk_cur + hf * 8);
+                p_half(vs, hf, masked_next, pk_cur + hf * 8);
             }
             if constexpr (!Cfg::kPAliasesS) {
                 ok = mbar_wait(p_free, it & 1, ctx, 52);  // dV(it) has consumed P^T(it): its columns can be rewritten
@@ -556,8 +573,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 }
 
 template <int D>
-int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, const float* lse2, const float* delta,
-                 float* dq_accum, void* dK, void* dV, const Shape& s, unsigned int* status, cudaStream_t stream) {
+int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
+                 const void* delta_cols, float* dq_accum, void* dK, void* dV, const Shape& s, unsigned int* status, cudaStream_t stream) {
     using Cfg = BwdCfg<D>;
     CUtensorMap mq, mk, mv, mdo;
     int rc = make_panel_tmap(&mq, Q, s.q_rows(), D, kTile);
@@ -571,11 +588,14 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     CUtensorMap mdq;
     rc = make_f32_box_tmap(&mdq, dq_accum, s.q_rows(), D, 32);
     if (rc) return rc;
+    CUtensorMap mlse, mdlt;
+    rc = make_col8_tmap(&mlse, lse_cols, s.q_rows(), kTile);
+    if (rc) return rc;
+    rc = make_col8_tmap(&mdlt, delta_cols, s.q_rows(), kTile);
+    if (rc) return rc;
     GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::kSmemTotal));
     BwdParams p;
-    p.lse2 = lse2;
-    p.delta = delta;
     p.dq_accum = dq_accum;
     p.dK = static_cast<__nv_bfloat16*>(dK);
     p.dV = static_cast<__nv_bfloat16*>(dV);
@@ -589,7 +609,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)(p.n_tiles * s.B * s.Hkv);
-    gqa_bwd_sm100_kernel<D><<<grid, kBwdThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, p);
+    gqa_bwd_sm100_kernel<D><<<grid, kBwdThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, mlse, mdlt, p);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;
@@ -603,11 +623,11 @@ extern "C" int gqa_debug_copy_bwd_trace(long long* host) {
 }
 #endif
 
-int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const float* lse2,
-                          const float* delta, float* dq_accum, void* dK, void* dV, const Shape& s,
+int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
+                          const void* delta_cols, float* dq_accum, void* dK, void* dV, const Shape& s,
                           unsigned int* status, cudaStream_t stream) {
-    if (s.D == 64) return launch_bwd_t<64>(Q, K, V, dO, lse2, delta, dq_accum, dK, dV, s, status, stream);
-    return launch_bwd_t<128>(Q, K, V, dO, lse2, delta, dq_accum, dK, dV, s, status, stream);
+    if (s.D == 64) return launch_bwd_t<64>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dK, dV, s, status, stream);
+    return launch_bwd_t<128>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dK, dV, s, status, stream);
 }
 
 }  // namespace gqa

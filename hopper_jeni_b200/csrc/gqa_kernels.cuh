@@ -16,20 +16,24 @@ struct Shape {
 
 // Workspace carve-up for the backward (offsets in bytes, 256-byte aligned).
 struct BwdWorkspace {
-    size_t status_off, delta_off, lse2_off, dq_accum_off, total;
+    // lse_cols / delta_cols: per query row eight bf16 (16 bytes): a three-way bf16 split of -LSE/scale and of
+    // -Delta in the first three, zeros after; they enter the S^T and dP^T products as one extra K step.
+    size_t status_off, lse_cols_off, delta_cols_off, dq_accum_off, total;
     explicit BwdWorkspace(const Shape& s) {
         auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
         status_off = 0;
-        delta_off = 256;
-        lse2_off = delta_off + up(s.q_rows() * sizeof(float));
-        dq_accum_off = lse2_off + up(s.q_rows() * sizeof(float));
+        lse_cols_off = 256;
+        delta_cols_off = lse_cols_off + up(s.q_rows() * 16);
+        dq_accum_off = delta_cols_off + up(s.q_rows() * 16);
         total = dq_accum_off + up(s.q_rows() * (size_t)s.D * sizeof(float));
     }
 };
 
-// Stage 1 of the backward: Delta, LSE*log2(e), zeroed dQ accumulator.
-int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float* delta, float* lse2, float* dq_accum,
-                          size_t rows, int D, cudaStream_t stream);
+// Stage 1 of the backward: Delta = rowsum(dO*O); with `delta` it is stored as fp32, with the column arrays
+// the bf16 splits of -LSE*inv_scale and -Delta are stored (16 bytes per row each) and, if given, the dQ
+// accumulator is zeroed.
+int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float inv_scale, float* delta,
+                          void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream);
 // Stage 3 of the backward: dQ = bf16(scale * dq_accum).
 int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream);
 
@@ -38,8 +42,8 @@ int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float
                      unsigned int* status, cudaStream_t stream);
 // Stage 2 of the backward: KV-tile-parallel main kernel (tcgen05 + TMEM + TMA); dK/dV written
 // once per element, dQ accumulated into dq_accum with fp32 reductions.
-int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const float* lse2,
-                          const float* delta, float* dq_accum, void* dK, void* dV, const Shape& s,
+int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
+                          const void* delta_cols, float* dq_accum, void* dK, void* dV, const Shape& s,
                           unsigned int* status, cudaStream_t stream);
 
 // CUDA-core checker kernels (slow, simple; fp32 math on bf16 inputs).

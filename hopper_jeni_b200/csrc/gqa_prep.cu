@@ -1,9 +1,10 @@
 // Memory-bound helper kernels around the tensor-core backward:
-//   * preprocess: Delta = rowsum(dO * O), LSE pre-multiplied by log2(e), and zeroing of
-//     the fp32 dQ accumulator, in one pass (stage 1 of the backward);
+//   * preprocess: Delta = rowsum(dO * O), the bf16 column splits of -LSE/scale and -Delta that the
+//     main kernel folds into its S^T and dP^T products, and zeroing of the fp32 dQ accumulator, in
+//     one pass (stage 1 of the backward);
 //   * finalise:   dQ = bf16(scale * dq_accum) (stage 3).
 // Algorithmic traffic per query row (D bf16 elements): preprocess reads 2*D*2 B and writes
-// D*4 + 8 B; finalise reads D*4 B and writes D*2 B.
+// D*4 + 32 B; finalise reads D*4 B and writes D*2 B.
 #include "gqa_common.cuh"
 #include "gqa_kernels.cuh"
 
@@ -11,15 +12,23 @@ namespace gqa {
 
 namespace {
 
-constexpr float kLog2e = 1.4426950408889634f;
+// x as hi + mid + lo with each part a bf16: exact to about 2^-24 relative; returned as {hi|mid<<16, lo}.
+__device__ __forceinline__ uint2 split3_bf16(float x) {
+    const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    return make_uint2((uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(mid) << 16),
+                      (uint32_t)__bfloat16_as_ushort(lo));
+}
 
 // One group of D/8 lanes per row; each lane owns 8 consecutive elements (one 16-byte load
 // from O and one from dO).  A warp covers 256/D rows per step.
 template <int D>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO, const float* __restrict__ lse,
-                      float* __restrict__ delta, float* __restrict__ lse2, float4* __restrict__ dq_accum,
-                      size_t rows) {
+                      float inv_scale, float* __restrict__ delta, uint4* __restrict__ lse_cols,
+                      uint4* __restrict__ delta_cols, float4* __restrict__ dq_accum, size_t rows) {
     constexpr int kLanesPerRow = D / 8;
     constexpr int kRowsPerWarp = 32 / kLanesPerRow;
     const int lane = threadIdx.x & 31;
@@ -47,8 +56,12 @@ bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO,
 #pragma unroll
         for (int off = kLanesPerRow / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
         if (row < rows && part == 0) {
-            delta[row] = acc;
-            if (lse2) lse2[row] = lse[row] * kLog2e;
+            if (delta) delta[row] = acc;
+            if (lse_cols) {
+                const uint2 l = split3_bf16(-lse[row] * inv_scale), d = split3_bf16(-acc);
+                lse_cols[row] = make_uint4(l.x, l.y, 0u, 0u);
+                delta_cols[row] = make_uint4(d.x, d.y, 0u, 0u);
+            }
         }
     }
 }
@@ -83,16 +96,20 @@ int grid_for(size_t work_items, int per_block) {
 
 }  // namespace
 
-int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float* delta, float* lse2, float* dq_accum,
-                          size_t rows, int D, cudaStream_t stream) {
+int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float inv_scale, float* delta,
+                          void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream) {
     const int rows_per_block = (256 / 32) * (256 / D);
     const int grid = grid_for(rows, rows_per_block);
     if (D == 64)
         bwd_preprocess_kernel<64><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
-                                                            lse, delta, lse2, reinterpret_cast<float4*>(dq_accum), rows);
+                                                            lse, inv_scale, delta, static_cast<uint4*>(lse_cols),
+                                                            static_cast<uint4*>(delta_cols),
+                                                            reinterpret_cast<float4*>(dq_accum), rows);
     else
         bwd_preprocess_kernel<128><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
-                                                             lse, delta, lse2, reinterpret_cast<float4*>(dq_accum), rows);
+                                                             lse, inv_scale, delta, static_cast<uint4*>(lse_cols),
+                                                            static_cast<uint4*>(delta_cols),
+                                                            reinterpret_cast<float4*>(dq_accum), rows);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;
@@ -114,6 +131,6 @@ extern "C" int gqa_bwd_delta(const void* O, const void* dO, float* delta, size_t
     if (!O || !dO || !delta || rows == 0) return GQA_ERR_BAD_ARGUMENT;
     if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
     if (!gqa::aligned16(O) || !gqa::aligned16(dO)) return GQA_ERR_BAD_ARGUMENT;
-    return gqa::launch_bwd_preprocess(O, dO, nullptr, delta, nullptr, nullptr, rows, D,
+    return gqa::launch_bwd_preprocess(O, dO, nullptr, 0.f, delta, nullptr, nullptr, nullptr, rows, D,
                                       reinterpret_cast<cudaStream_t>(stream));
 }

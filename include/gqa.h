@@ -55,8 +55,8 @@ int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE,
                gqa_stream_t stream);
 
 /*
- * Bytes of device scratch gqa_bwd needs for this shape (Delta, the fp32 dQ
- * accumulator and a status word).  The reference keeps the same buffers as
+* Bytes of device scratch gqa_bwd needs for this shape (per-row LSE and Delta terms,
+ * the fp32 dQ accumulator and a status word).  The reference keeps the same buffers as
  * function-static allocations inside its launcher
  * (src/attention/GQA_bwd_baseline.cu:579-587); here the caller owns them.
  */
@@ -91,7 +91,7 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
  *
  *  - Shapes whose scratch (gqa_bwd_workspace_bytes) exceeds the array are refused with
  *    GQA_ERR_WORKSPACE and an explanation in gqa_last_cuda_error(); nothing is launched.
- *    32 MiB covers e.g. B*Hq*S <= 126 976 rows at D = 64 or 64 512 rows at D = 128.
+ *    32 MiB covers e.g. B*Hq*S <= 114 688 rows at D = 64 or 61 440 rows at D = 128.
  *  - It calls no cudaMalloc/cudaFree and no allocating library routine.
  *  - The first call on each device looks up the array's device address (one runtime
  *    query, no allocation).  Make that first call outside any stream capture.
