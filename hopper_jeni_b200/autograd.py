@@ -1,0 +1,32 @@
+"""``torch.autograd.Function`` over the C ABI: forward keeps O and LSE for the backward, so the backward
+does not recompute the forward (the hand-off the reference does through files, src/attention/GQA_bwd_baseline.cu:641-643)."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import ops
+
+
+class _GqaAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = ops.gqa_forward(q, k, v, causal=causal, scale=scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ops.gqa_backward(q, k, v, o, do.contiguous(), lse, causal=ctx.causal, scale=ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def gqa_attention(q, k, v, causal: bool = False, scale: float | None = None):
+    """Differentiable GQA attention on bf16 CUDA tensors ``[B,Hq,S,D]`` / ``[B,Hkv,S,D]``; same semantics as
+    ``F.scaled_dot_product_attention(q, k, v, scale=scale, is_causal=causal, enable_gqa=True)``."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else float(scale)
+    return _GqaAttention.apply(q, k, v, bool(causal), scale)

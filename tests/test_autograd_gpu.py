@@ -1,0 +1,23 @@
+"""GPU test: the autograd wrapper against PyTorch fp32 SDPA autograd (the reference's oracle call,
+precision/baseline_gqa.py:64-66, :429-435) on the same seeded inputs."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import util
+from hopper_jeni_b200.autograd import gqa_attention
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_autograd_wrapper_matches_fp32_sdpa(gqa_lib, causal):
+    B, Hq, Hkv, S, D = 2, 8, 2, 512, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v = (torch.randn(B, h, S, D, generator=g, device="cuda").bfloat16().requires_grad_(True) for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, Hq, S, D, generator=g, device="cuda").bfloat16()
+    gqa_attention(q, k, v, causal=causal).backward(do)
+    q32, k32, v32 = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    F.scaled_dot_product_attention(q32, k32, v32, is_causal=causal, enable_gqa=True).backward(do.float())
+    for got, ref, name in ((q.grad, q32.grad, "dQ"), (k.grad, k32.grad, "dK"), (v.grad, v32.grad, "dV")):
+        util.assert_close_bf16(util.to_np(got), util.to_np(ref), name, util.REL_RMS_BWD)
