@@ -43,14 +43,20 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
+// One try: returns at once when the phase has completed, otherwise the hardware may park the thread until the
+// phase completes or the hint (nanoseconds) runs out, so that waiting role warps need not spin on issue slots
+// (measured neutral against the default on B200, kept for the intent).
+#ifndef GQA_MBAR_SUSPEND_NS
+#define GQA_MBAR_SUSPEND_NS 10000
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)GQA_MBAR_SUSPEND_NS)
         : "memory");
     return ok != 0;
 }

@@ -2,7 +2,7 @@
 
 Run once in a container that has the reference checkout (read-only) and torch on CPU:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path-to-reference-checkout>
 
 It imports, unmodified, the reference's
   * ``fp64_reference`` / ``fp64_backward``   (precision/baseline_gqa.py:40-61, :169-197; causal only)
@@ -86,4 +86,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path-to-reference-checkout>")
+    main(sys.argv[1])
