@@ -448,14 +448,12 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             for (int q2 = 0; q2 < 2; ++q2) {
                 const uint32_t* pp = pk + q2 * 4;
                 uint4 o;
-                o.x = pack_bf16x2(bf16_lo_to_f32(pp[0]) * __uint_as_float(v[q2 * 8 + 0]),
-                                  bf16_hi_to_f32(pp[0]) * __uint_as_float(v[q2 * 8 + 1]));
-                o.y = pack_bf16x2(bf16_lo_to_f32(pp[1]) * __uint_as_float(v[q2 * 8 + 2]),
-                                  bf16_hi_to_f32(pp[1]) * __uint_as_float(v[q2 * 8 + 3]));
-                o.z = pack_bf16x2(bf16_lo_to_f32(pp[2]) * __uint_as_float(v[q2 * 8 + 4]),
-                                  bf16_hi_to_f32(pp[2]) * __uint_as_float(v[q2 * 8 + 5]));
-                o.w = pack_bf16x2(bf16_lo_to_f32(pp[3]) * __uint_as_float(v[q2 * 8 + 6]),
-                                  bf16_hi_to_f32(pp[3]) * __uint_as_float(v[q2 * 8 + 7]));
+                // (dP - Delta) is rounded to bf16 and multiplied with the bf16 P in one packed instruction: three
+                // instructions per pair instead of five; measured +3 % speed, relative RMS error of dQ/dK 2.9e-3 -> 3.4e-3
+                o.x = mul_bf16x2(pp[0], pack_bf16x2(__uint_as_float(v[q2 * 8 + 0]), __uint_as_float(v[q2 * 8 + 1])));
+                o.y = mul_bf16x2(pp[1], pack_bf16x2(__uint_as_float(v[q2 * 8 + 2]), __uint_as_float(v[q2 * 8 + 3])));
+                o.z = mul_bf16x2(pp[2], pack_bf16x2(__uint_as_float(v[q2 * 8 + 4]), __uint_as_float(v[q2 * 8 + 5])));
+                o.w = mul_bf16x2(pp[3], pack_bf16x2(__uint_as_float(v[q2 * 8 + 6]), __uint_as_float(v[q2 * 8 + 7])));
                 const int chunk = chunk0 + hf * 2 + q2;
                 *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
                 dsp[q2 * 4 + 0] = o.x;
