@@ -19,7 +19,7 @@
 //   dK  += dS^T Q      (A = dS^T K-major, B = Q panel read MN-major)
 //   dQ   = dS K        (A = dS^T read MN-major, B = K panel read MN-major)
 //
-// Roles (25 warps):
+// Roles at D = 64 (25 warps; D = 128 uses 16: two elementwise warpgroups, dK and dQ from one issuer):
 //   warps 0-3    drain dQ tiles from TMEM into the fp32 accumulator
 //   warps 4-19   four elementwise warpgroups; each owns 32 query columns of the tile pair
 //   warp  20     TMA producer
@@ -57,15 +57,28 @@ __device__ long long g_bwd_trace[3][64][4];
 
 constexpr int kTile = 128;
 constexpr int kPanel = kTile * 128;  // bytes of one 64-column panel of a 128-row tile
-constexpr int kBwdThreads = 800;
-constexpr int kWarpEw0 = 4, kWarpTma = 20, kWarpMmaS = 21, kWarpMmaDV = 22, kWarpMmaDK = 23,
-              kWarpMmaDQ = 24;
-constexpr int kEwThreads = 512;
+constexpr int kWarpEw0 = 4;  // warps 0-3 drain dQ, the elementwise warpgroups follow
 
 template <int D>
 struct BwdCfg {
     static constexpr int kPanels = D / 64;
     static constexpr int kTileBytes = kPanels * kPanel;
+    // Elementwise warpgroups: four at D = 64 (32 query columns per thread).  At D = 128 two (64 columns per
+    // thread): the tensor work per tile pair doubles while the elementwise work does not, and the smaller CTA
+    // (16 instead of 25 warps) leaves 128 registers per thread, which the dQ drain needs (see kDrainEarlyRelease).
+    static constexpr int kEwGroups = (D == 64) ? 4 : 2;
+    static constexpr int kCols = kTile / kEwGroups;       // query columns per elementwise thread
+    static constexpr int kHalves = kCols / 16;            // 16-column steps per thread and stage
+    static constexpr int kEwThreads = kEwGroups * 128;
+    // D = 128: dK and dQ (both wait for dS^T) are issued by one warp, which makes the CTA exactly 16 warps.
+    static constexpr bool kMergeDkDq = (D == 128);
+    static constexpr int kWarpTma = kWarpEw0 + 4 * kEwGroups, kWarpMmaS = kWarpTma + 1, kWarpMmaDV = kWarpTma + 2,
+                         kWarpMmaDK = kWarpTma + 3, kWarpMmaDQ = kMergeDkDq ? kWarpMmaDK : kWarpTma + 4;
+    static constexpr int kThreads = (kWarpMmaDQ + 1) * 32;
+    // D = 128: dQ sits in the dP^T columns, so the next dP^T product waits for the drain.  The drain warps
+    // therefore pull the tile into registers as fast as TMEM delivers it (three 32-column chunks at once, the
+    // fourth as soon as the first is staged) and hand the columns back before the copy engine has taken anything.
+    static constexpr bool kDrainEarlyRelease = (D == 128);
     static constexpr int kQStages = 2;
     static constexpr int kDOStages = (D == 64) ? 2 : 1;
     static constexpr int kColPanel = kTile * 16;  // 128 rows x 16 B: an un-swizzled 8-column operand panel
@@ -113,12 +126,13 @@ struct BwdParams {
 template <int D>
 __device__ __forceinline__ uint32_t p_col_of_kstep(int kk) {
     using Cfg = BwdCfg<D>;
-    if constexpr (Cfg::kPAliasesS) return Cfg::kColS + (kk >> 1) * 32 + (kk & 1) * 8;  // inside its owner's S columns
+    if constexpr (Cfg::kPAliasesS)  // inside its owner's S columns
+        return Cfg::kColS + (kk / Cfg::kHalves) * Cfg::kCols + (kk % Cfg::kHalves) * 8;
     else return Cfg::kColP + kk * 8;
 }
 
 template <int D>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapDQ, const __grid_constant__ CUtensorMap mapLseCol,
@@ -182,8 +196,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         mbar_init(kv_full, 1);
         mbar_init(s_full, 1);
         mbar_init(dp_full, 1);
-        mbar_init(p_ready, kEwThreads);
-        mbar_init(ds_ready, kEwThreads);
+        mbar_init(p_ready, Cfg::kEwThreads);
+        mbar_init(ds_ready, Cfg::kEwThreads);
         mbar_init(p_free, 1);
         mbar_init(ds_free, 2);
         mbar_init(dq_full, 1);
@@ -199,7 +213,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
         fence_mbar_init();
     }
-    if (warp == kWarpMmaS) {
+    if (warp == Cfg::kWarpMmaS) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -215,7 +229,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ);
     const uint32_t do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
 
-    if (warp == kWarpTma) {
+    if (warp == Cfg::kWarpTma) {
         // ======================= TMA producer =======================
         if (elect_one()) {
             tma_prefetch_desc(&mapQ);
@@ -254,7 +268,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 }
             }
         }
-    } else if (warp == kWarpMmaS) {
+    } else if (warp == Cfg::kWarpMmaS) {
         // ======================= issuer: S^T(it) = K Q^T, dP^T(it) = V dO^T =======================
         // The whole warp runs the loop (uniform control flow); `leader` marks the one lane that issues.
         const uint32_t leader = elect_one() ? 1u : 0u;
@@ -296,7 +310,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             umma_commit_pred(leader, &do_empty[dos]);
             GQA_TRACE(1, it, 1);
         }
-    } else if (warp == kWarpMmaDV) {
+    } else if (warp == Cfg::kWarpMmaDV) {
         // ======================= issuer: dV += P^T dO(it)  (A from TMEM, B = dO read MN-major) =======================
         const uint32_t leader = elect_one() ? 1u : 0u;
         const uint32_t idesc = make_idesc_bf16(128, D, false, true);
@@ -316,11 +330,11 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             GQA_TRACE(1, it, 2);
         }
         if (ok) umma_commit_pred(leader, acc_full);
-    } else if (warp == kWarpMmaDK) {
+    } else if (warp == Cfg::kWarpMmaDK) {
         // ======================= issuer: dK += dS^T Q(it)  (A = dS^T K-major, B = Q read MN-major) =======================
         const uint32_t leader = elect_one() ? 1u : 0u;
         const uint32_t idesc = make_idesc_bf16(128, D, false, true);
-        bool ok = true;
+        bool ok = Cfg::kMergeDkDq ? mbar_wait(kv_full, 0, ctx, 34) : true;
         for (int it = 0; it < n_iter && ok; ++it) {
             const int qs = it % Cfg::kQStages;
             ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 32) && mbar_wait(ds_ready, it & 1, ctx, 33);
@@ -330,7 +344,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 if constexpr (Cfg::kDsInTmem)  // A = bf16 dS^T in the dP^T columns: query columns [16kk, 16kk+16)
-                    umma_ts_pred(leader, tmem + Cfg::kColDK, tmem + Cfg::kColDP + (kk >> 1) * 32 + (kk & 1) * 8,
+                    umma_ts_pred(leader, tmem + Cfg::kColDK, tmem + Cfg::kColDP + (kk / Cfg::kHalves) * Cfg::kCols + (kk % Cfg::kHalves) * 8,
                                  make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
                 else
                     umma_ss_pred(leader, tmem + Cfg::kColDK,
@@ -339,9 +353,22 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             }
             umma_commit_pred(leader, ds_free);
             umma_commit_pred(leader, &q_empty[qs]);
+            if constexpr (Cfg::kMergeDkDq) {  // dQ(it) = dS K from the same warp
+                if (it > 0) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 36);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_ss_pred(leader, tmem + Cfg::kColDQ, make_sdesc_sw128(ds_addr + kk * 2048, kPanel, 1024),
+                                 make_sdesc_sw128(k_addr + kk * 2048, kPanel, 1024), idesc_dq, kk > 0);
+                umma_commit_pred(leader, dq_full);
+                umma_commit_pred(leader, ds_free);
+                GQA_TRACE(1, it, 3);
+            }
         }
         if (ok) umma_commit_pred(leader, acc_full);
-    } else if (warp == kWarpMmaDQ) {
+    } else if (!Cfg::kMergeDkDq && warp == Cfg::kWarpMmaDQ) {
         // ======================= issuer: dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major) =======================
         const uint32_t leader = elect_one() ? 1u : 0u;
         const uint32_t idesc = make_idesc_bf16(128, D, true, true);
@@ -373,54 +400,93 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             GQA_TRACE(2, it, 0);
             const int row = q_row_of(it) + warp * 32;
             constexpr int kRounds = D / (32 * Cfg::kDqBoxes);
-#pragma unroll 1
-            for (int rnd = 0; rnd < kRounds; ++rnd) {
-#pragma unroll
-                for (int bx = 0; bx < Cfg::kDqBoxes; ++bx) {
-                    uint32_t v[32];
-                    tmem_ld32(tDQ + (rnd * Cfg::kDqBoxes + bx) * 32, v);
-                    tmem_wait_ld();
-                    if (rnd == kRounds - 1 && bx == Cfg::kDqBoxes - 1) {  // every column is in registers: hand the TMEM tile back
-                        tc_fence_before_sync();
-                        mbar_arrive(dq_empty);
-                    }
+            if constexpr (Cfg::kDrainEarlyRelease) {
+                static_assert(!Cfg::kDrainEarlyRelease || (D == 128 && Cfg::kDqBoxes == 1), "four 32-column chunks, one box");
+                auto stage_and_reduce = [&](const uint32_t (&v)[32], int chunk) {
 #pragma unroll
                     for (int c8 = 0; c8 < 8; ++c8)
-                        *reinterpret_cast<uint4*>(stage + bx * 4096 + ((c8 ^ sw) << 4)) =
+                        *reinterpret_cast<uint4*>(stage + ((c8 ^ sw) << 4)) =
                             make_uint4(v[4 * c8], v[4 * c8 + 1], v[4 * c8 + 2], v[4 * c8 + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage, chunk * 32, row);
+                        bulk_commit_group();
+                    }
+                };
+                auto wait_box_free = [&]() {
+                    if (lane == 0) bulk_wait_read_all();
+                    __syncwarp();
+                };
+                uint32_t va[32], vb[32], vc[32];
+                tmem_ld32(tDQ, va);
+                tmem_ld32(tDQ + 32, vb);
+                tmem_ld32(tDQ + 64, vc);
+                tmem_wait_ld();
+                stage_and_reduce(va, 0);
+                tmem_ld32(tDQ + 96, va);  // chunk 0 is in shared memory: its registers take chunk 3
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(dq_empty);     // the dP^T columns are free after two TMEM round trips
+                wait_box_free();
+                stage_and_reduce(vb, 1);
+                wait_box_free();
+                stage_and_reduce(vc, 2);
+                wait_box_free();
+                stage_and_reduce(va, 3);
+                wait_box_free();
+            } else {
+    #pragma unroll 1
+                for (int rnd = 0; rnd < kRounds; ++rnd) {
+    #pragma unroll
+                    for (int bx = 0; bx < Cfg::kDqBoxes; ++bx) {
+                        uint32_t v[32];
+                        tmem_ld32(tDQ + (rnd * Cfg::kDqBoxes + bx) * 32, v);
+                        tmem_wait_ld();
+                        if (rnd == kRounds - 1 && bx == Cfg::kDqBoxes - 1) {  // every column is in registers: hand the TMEM tile back
+                            tc_fence_before_sync();
+                            mbar_arrive(dq_empty);
+                        }
+    #pragma unroll
+                        for (int c8 = 0; c8 < 8; ++c8)
+                            *reinterpret_cast<uint4*>(stage + bx * 4096 + ((c8 ^ sw) << 4)) =
+                                make_uint4(v[4 * c8], v[4 * c8 + 1], v[4 * c8 + 2], v[4 * c8 + 3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+    #pragma unroll
+                        for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)
+                            tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage + bx * 4096, (rnd * Cfg::kDqBoxes + bx) * 32, row);
+                        bulk_commit_group();
+                        bulk_wait_read_all();  // staging boxes may be overwritten after this
+                    }
+                    __syncwarp();
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-#pragma unroll
-                    for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)
-                        tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage + bx * 4096, (rnd * Cfg::kDqBoxes + bx) * 32, row);
-                    bulk_commit_group();
-                    bulk_wait_read_all();  // staging boxes may be overwritten after this
-                }
-                __syncwarp();
             }
             GQA_TRACE(2, it, 1);
         }
         if (lane == 0) bulk_wait_all();
-    } else if (warp < kWarpTma) {
+    } else if (warp < Cfg::kWarpTma) {
         // ======================= elementwise warpgroups (P^T and dS^T) =======================
         // Rotated by half an iteration: the body of iteration `it` turns dP^T(it) into dS^T(it) and then
         // S^T(it+1) into P^T(it+1); P^T is carried in registers as packed bf16 (the rounded values the
         // dV product uses) between the two halves.
-        const int w = (warp - kWarpEw0) >> 2;     // which 32 query columns of the tile pair
+        constexpr int C = Cfg::kCols, H = Cfg::kHalves;
+        const int w = (warp - kWarpEw0) >> 2;     // which C query columns of the tile pair
         const int j = (warp & 3) * 32 + lane;     // key row inside the tile == TMEM lane
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tS = tmem + lane_addr + Cfg::kColS + w * 32;
-        const uint32_t tDP = tmem + lane_addr + Cfg::kColDP + w * 32;
-        const uint32_t tP = tmem + lane_addr + (Cfg::kPAliasesS ? (Cfg::kColS + w * 32) : (Cfg::kColP + w * 16));
-        // dS^T row j, query columns [32w, 32w+32): panel w/2, 16-byte chunks (w&1)*4 .. +3
-        uint8_t* ds_row = sDS + (w >> 1) * kPanel + j * 128;
-        const int chunk0 = (w & 1) * 4;
+        const uint32_t tS = tmem + lane_addr + Cfg::kColS + w * C;
+        const uint32_t tDP = tmem + lane_addr + Cfg::kColDP + w * C;
+        const uint32_t tP = tmem + lane_addr + (Cfg::kPAliasesS ? (Cfg::kColS + w * C) : (Cfg::kColP + w * (C / 2)));
+        // dS^T row j, query columns [C*w, C*w+C): 64-column panel (C*w)/64, 16-byte chunks from ((C*w) % 64)/8 on
+        uint8_t* ds_row = sDS + ((w * C) >> 6) * kPanel + j * 128;
+        const int chunk0 = ((w * C) & 63) >> 3;
         const float c = p.scale_log2;
         const bool trace_me = (warp == kWarpEw0);
+        (void)trace_me;
         bool ok = true;
-        uint32_t pk_cur[16];  // P^T(it) of this thread: 32 query columns as packed bf16 pairs
+        uint32_t pk_cur[C / 2];  // P^T(it) of this thread: C query columns as packed bf16 pairs
 
         // P^T of 16 columns [16*hf, 16*hf+16) from the S^T values v (which already hold S - LSE/scale) -> packed pairs
         auto p_half = [&](const uint32_t (&v)[16], int hf, bool masked, uint32_t* out) {
@@ -431,7 +497,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 float e2 = ex2_approx(__uint_as_float(v[4 * i + 2]) * c);
                 float e3 = ex2_approx(__uint_as_float(v[4 * i + 3]) * c);
                 if (masked) {  // key j is visible to query i iff j <= i
-                    const int col = w * 32 + hf * 16 + 4 * i;
+                    const int col = w * C + hf * 16 + 4 * i;
                     if (j > col + 0) e0 = 0.f;
                     if (j > col + 1) e1 = 0.f;
                     if (j > col + 2) e2 = 0.f;
@@ -462,8 +528,14 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 dsp[q2 * 4 + 3] = o.w;
             }
         };
-        auto publish_p = [&](const uint32_t (&pk)[16]) {
-            tmem_st16(tP, pk);
+        auto publish_p = [&](const uint32_t* pk) {
+#pragma unroll
+            for (int ch = 0; ch < C / 32; ++ch) {
+                uint32_t t16[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) t16[i] = pk[ch * 16 + i];
+                tmem_st16(tP + ch * 16, t16);
+            }
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_ready);
@@ -475,7 +547,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tc_fence_after_sync();
             const bool masked0 = p.causal != 0;  // iteration 0 is the diagonal tile when causal
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
+            for (int hf = 0; hf < H; ++hf) {
                 uint32_t v[16];
                 tmem_ld16(tS + hf * 16, v);
                 tmem_wait_ld();
@@ -493,16 +565,20 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tc_fence_after_sync();
             if (trace_me) GQA_TRACE(0, it, 0);
             {
-                uint32_t dsp[16];
+                uint32_t dsp[C / 2];
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
+                for (int hf = 0; hf < H; ++hf) {
                     uint32_t vd[16];
                     tmem_ld16(tDP + hf * 16, vd);
                     tmem_wait_ld();
                     ds_half(vd, hf, pk_cur + hf * 8, dsp + hf * 8);
                 }
                 if constexpr (Cfg::kDsInTmem) {
-                    tmem_st16(tDP, dsp);  // over this thread's own, already consumed, dP^T columns
+                    static_assert(!Cfg::kDsInTmem || C == 32, "the TMEM copy of dS^T is written as one 16-column store");
+                    uint32_t t16[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) t16[i] = dsp[i];
+                    tmem_st16(tDP, t16);  // over this thread's own, already consumed, dP^T columns
                     tmem_wait_st();
                 }
             }
@@ -517,7 +593,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tc_fence_after_sync();
             if (trace_me) GQA_TRACE(0, it, 2);
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
+            for (int hf = 0; hf < H; ++hf) {
                 uint32_t vs[16];
                 tmem_ld16(tS + hf * 16, vs);
                 tmem_wait_ld();
@@ -535,7 +611,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (ok) ok = mbar_wait(acc_full, 0, ctx, 55);
         if (ok) {
             tc_fence_after_sync();
-            constexpr int kQuarter = D / 4;  // 16 or 32 columns
+            constexpr int kQuarter = D / Cfg::kEwGroups;  // columns of dV / dK per warpgroup
             const size_t grow = (size_t)kv_row0 + j;
 #pragma unroll 1
             for (int which = 0; which < 2; ++which) {
@@ -564,7 +640,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // ---- teardown ---------------------------------------------------------------
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == kWarpMmaS) {
+    if (warp == Cfg::kWarpMmaS) {
         if (*abort_flag != 0) __nanosleep(20000);  // let in-flight copies and MMAs drain before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
@@ -607,7 +683,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)(p.n_tiles * s.B * s.Hkv);
-    gqa_bwd_sm100_kernel<D><<<grid, kBwdThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, mlse, mdlt, p);
+    gqa_bwd_sm100_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, mlse, mdlt, p);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;

@@ -46,7 +46,8 @@ def test_static_scratch_backward_matches_gqa_bwd_twice(gqa_lib, shape, causal):
         rc = _call_static(gqa_lib, tq, tk, tv, o, tdo, lse, dq, dk, dv, causal, sc)
         capi.check("gqa_bwd_static_scratch", rc)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        # no growth of the torch allocator around the call (it may shrink: Python can free earlier temporaries)
+        assert torch.cuda.memory_allocated() <= before
         # dK and dV have one writer per element in both entry points: identical bits.  dQ is summed with
         # fp32 atomics in an order that changes from run to run: the bf16 parity tolerance applies.
         assert torch.equal(dk, dk_ref) and torch.equal(dv, dv_ref)
