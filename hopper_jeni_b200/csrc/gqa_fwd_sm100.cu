@@ -5,14 +5,15 @@
 //   warps 0-3  softmax warpgroup for query tile 0 (thread = query row = TMEM lane)
 //   warps 4-7  softmax warpgroup for query tile 1
 //   warp  8    TMA producer (Q once, K and V rings)
-//   warp  9    UMMA issuer for S = Q K^T (both tiles)
-//   warps 10,11 UMMA issuers for O += P V of tile 0 / tile 1 (P read from TMEM)
-// One issuing warp sustains a product with A in TMEM only every ~78 cycles, and the three GEMM
-// streams wait on different producers, hence three issuers (warp-uniform loops, one elected lane).  The two query tiles ping-pong: while one warpgroup runs its softmax (the exp unit is
-// the bound at D = 64), the tensor core works on the other tile.  S lives in TMEM (128 fp32 columns per tile), P
-// overwrites the first 64 columns of S as packed bf16, O accumulates in TMEM.
-// The running maximum is only refreshed when it grows by more than 2^8, so O is
-// rescaled rarely; the final division by the row sum uses the same maximum.
+//   warps 9,10 UMMA issuers, one per query tile: S = Q K^T and O += P V (P read from TMEM)
+// Every key block is handled as two half-blocks of 64 keys, and the 128 fp32 S columns of a tile are two
+// 64-column buffers: while the softmax warpgroup works on half-block j, the issuer has already produced
+// S(j+1) in the other buffer, so the warpgroup never waits for the tensor core in steady state (with one
+// 128-column S buffer per tile the chain softmax -> P V -> Q K^T -> softmax was serial and set the period).
+// P(j) overwrites the first 32 columns of its own S buffer as packed bf16; S(j+2) may overwrite it only after
+// P(j) V has completed (pv_done barrier; different accumulators, so issue order alone guarantees nothing).
+// The running maximum is only refreshed when it grows by more than 2^8, so O is rescaled rarely (and then
+// only after the previous P V has completed); the final division by the row sum uses the same maximum.
 //
 // Replaces gqa62::gqa_v62 / launch_gqa_v62 (src/attention/GQA_fwd_ref.cu:336-651):
 // same inputs/outputs, LSE = natural-log of the scaled-logit sum (:611-614).
@@ -27,7 +28,7 @@ using namespace sm100;
 
 // Optional timeline tracing (development builds only): block 0 stamps clock64 at a few points per key block.
 #ifdef GQA_FWD_TRACE
-__device__ long long g_fwd_trace[3][64][4];
+__device__ long long g_fwd_trace[6][64][4];
 #define GQA_FTRACE(role, it, slot)                                                                 \
     do {                                                                                           \
         if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (it) < 64 && (threadIdx.x & 31) == 0) \
@@ -41,8 +42,9 @@ __device__ long long g_fwd_trace[3][64][4];
 
 constexpr int kTile = 128;             // query rows per tile and key rows per block
 constexpr int kPanel = kTile * 128;    // bytes of one 64-column panel of a 128-row tile
-constexpr int kFwdThreads = 384;
-constexpr int kWarpTma = 8, kWarpQK = 9, kWarpPV0 = 10;
+constexpr int kHalf = 64;               // keys per half-block
+constexpr int kFwdThreads = 352;
+constexpr int kWarpTma = 8, kWarpMma0 = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
@@ -85,13 +87,12 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     uint8_t* sK = sQ + Cfg::kSmemQ;
     uint8_t* sV = sK + Cfg::kStages * Cfg::kTileBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + Cfg::kStages * Cfg::kTileBytes);
-    uint64_t* q_full = bars;                       // [2]
-    uint64_t* s_full = bars + 2;                   // [2]
-    uint64_t* p_full = bars + 4;                   // [2]
-    uint64_t* o_full = bars + 6;                   // [2]
-    uint64_t* pv_done = bars + 8;                  // [2] PV issuer t -> QK issuer: P_t consumed, S_t may be rewritten
-    uint64_t* turn = bars + 10;                    // [2] softmax warpgroup t finished the exp phase of a block
-    uint64_t* k_full = bars + 12;                  // [kStages]
+    uint64_t* q_full = bars;                       // [2]  per tile
+    uint64_t* o_full = bars + 2;                   // [2]  per tile
+    uint64_t* s_full = bars + 4;                   // [4]  per (tile, S buffer): S(j) written
+    uint64_t* p_full = bars + 8;                   // [4]  per (tile, S buffer): P(j) written by the warpgroup
+    uint64_t* pv_done = bars + 12;                 // [4]  per (tile, S buffer): P(j) V completed
+    uint64_t* k_full = bars + 16;                  // [kStages]
     uint64_t* k_empty = k_full + Cfg::kStages;     // [kStages]
     uint64_t* v_full = k_empty + Cfg::kStages;     // [kStages]
     uint64_t* v_empty = v_full + Cfg::kStages;     // [kStages]
@@ -122,21 +123,22 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
             mbar_init(&q_full[i], 1);
+            mbar_init(&o_full[i], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
-            mbar_init(&o_full[i], 1);
             mbar_init(&pv_done[i], 1);
-            mbar_init(&turn[i], 128);
         }
         for (int i = 0; i < Cfg::kStages; ++i) {
             mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
+            mbar_init(&k_empty[i], n_tiles);  // one commit per issuer that uses the block
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], n_tiles);  // one commit per PV issuer that uses the block
+            mbar_init(&v_empty[i], n_tiles);
         }
         fence_mbar_init();
     }
-    if (warp == kWarpQK) {
+    if (warp == kWarpMma0) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -169,58 +171,58 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     tma_load_2d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], pn * 64, kv_row0 + n * kTile);
             }
         }
-    } else if (warp == kWarpQK) {
-        // ======================= issuer: S_t(n) = Q_t K(n)^T for both tiles =======================
+    } else if (warp >= kWarpMma0) {
+        // ======================= issuer of tile t: S(j) = Q K(j)^T per half-block, O += P(j) V(j) =======================
         // The whole warp runs the loop (uniform control flow); `leader` marks the one lane that issues.
-        const uint32_t leader = elect_one() ? 1u : 0u;
-        const uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
-        const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK);
-        bool ok = true;
-        for (int t = 0; t < n_tiles && ok; ++t) ok = mbar_wait(&q_full[t], 0, ctx, 20);
-        for (int n = 0; n < n_max && ok; ++n) {
-            const int st = n % Cfg::kStages;
-            ok = mbar_wait(&k_full[st], (n / Cfg::kStages) & 1, ctx, 21);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                if (n >= n_blk[t]) continue;
-                if (n > 0) ok = mbar_wait(&pv_done[t], (n - 1) & 1, ctx, 22);  // P_t(n-1) lives in the S_t columns
-                if (!ok) break;
+        const int t = warp - kWarpMma0;
+        if (t < n_tiles) {
+            const uint32_t leader = elect_one() ? 1u : 0u;
+            const uint32_t idesc_qk = make_idesc_bf16(128, kHalf, false, false);
+            const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
+            const uint32_t q_addr = smem_u32(sQ) + t * Cfg::kTileBytes, k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            const uint32_t colS = tmem + (t ? Cfg::kColS1 : Cfg::kColS0), colO = tmem + (t ? Cfg::kColO1 : Cfg::kColO0);
+            const int total = 2 * n_blk[t];
+            bool ok = mbar_wait(&q_full[t], 0, ctx, 20);
+            // S(j): rows 64h.. of key block n = j/2 are the B operand (K-major panels, 64 rows = 8192 bytes down)
+            auto issue_qk = [&](int j) -> bool {
+                const int n = j >> 1, h = j & 1, st = n % Cfg::kStages;
+                if (h == 0 && !mbar_wait(&k_full[st], (n / Cfg::kStages) & 1, ctx, 21)) return false;
                 tc_fence_after_sync();
-                const uint32_t a0 = q_addr + t * Cfg::kTileBytes, b0 = k_addr + st * Cfg::kTileBytes;
+                const uint32_t b0 = k_addr + st * Cfg::kTileBytes + h * (kHalf * 128);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kPanel + (kk & 3) * 32;
-                    umma_ss_pred(leader, tmem + (t ? Cfg::kColS1 : Cfg::kColS0), make_sdesc_sw128(a0 + off, 16, 1024),
+                    umma_ss_pred(leader, colS + h * kHalf, make_sdesc_sw128(q_addr + off, 16, 1024),
                                  make_sdesc_sw128(b0 + off, 16, 1024), idesc_qk, kk > 0);
                 }
-                umma_commit_pred(leader, &s_full[t]);
-                if (t == 0) GQA_FTRACE(1, n, 0);
-            }
-            if (ok) umma_commit_pred(leader, &k_empty[st]);
-        }
-    } else if (warp >= kWarpPV0) {
-        // ======================= issuers: O_t += P_t(n) V(n)  (A = P_t from TMEM, B = V read MN-major) =======================
-        const int t = warp - kWarpPV0;
-        if (t < n_tiles) {
-            const uint32_t leader = elect_one() ? 1u : 0u;
-            const uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
-            const uint32_t v_addr = smem_u32(sV);
-            const uint32_t colS = t ? Cfg::kColS1 : Cfg::kColS0, colO = t ? Cfg::kColO1 : Cfg::kColO0;
-            bool ok = true;
-            for (int n = 0; n < n_blk[t] && ok; ++n) {
-                const int st = n % Cfg::kStages;
-                ok = mbar_wait(&v_full[st], (n / Cfg::kStages) & 1, ctx, 23) && mbar_wait(&p_full[t], n & 1, ctx, 24);
+                umma_commit_pred(leader, &s_full[t * 2 + h]);
+                if (h == 1) umma_commit_pred(leader, &k_empty[st]);
+                if (t == 0) GQA_FTRACE(1, j, 0);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < total && ok; ++j) {
+                const int n = j >> 1, h = j & 1, st = n % Cfg::kStages;
+                if (j + 1 < total) {
+                    // S(j+1) goes where P(j-1) lives: that product must have completed
+                    if (j >= 1) ok = mbar_wait(&pv_done[t * 2 + (h ^ 1)], ((j - 1) >> 1) & 1, ctx, 22);
+                    if (ok) ok = issue_qk(j + 1);
+                    if (!ok) break;
+                }
+                if (h == 0) ok = mbar_wait(&v_full[st], (n / Cfg::kStages) & 1, ctx, 23);
+                if (ok) ok = mbar_wait(&p_full[t * 2 + h], n & 1, ctx, 24);
                 if (!ok) break;
                 tc_fence_after_sync();
-                if (t == 0) GQA_FTRACE(1, n, 1);
-                const uint32_t b0 = v_addr + st * Cfg::kTileBytes;
+                if (t == 0) GQA_FTRACE(1, j, 1);
+                const uint32_t b0 = v_addr + st * Cfg::kTileBytes + h * (kHalf / 16) * 2048;
 #pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk)
-                    umma_ts_pred(leader, tmem + colO, tmem + colS + kk * 8, make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024),
-                                 idesc_pv, (n > 0 || kk > 0));
-                umma_commit_pred(leader, &pv_done[t]);
-                umma_commit_pred(leader, &v_empty[st]);
-                if (n + 1 == n_blk[t]) umma_commit_pred(leader, &o_full[t]);
-                if (t == 0) GQA_FTRACE(1, n, 2);
+                for (int kk = 0; kk < kHalf / 16; ++kk)
+                    umma_ts_pred(leader, colO, colS + h * kHalf + kk * 8, make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024),
+                                 idesc_pv, (j > 0 || kk > 0));
+                umma_commit_pred(leader, &pv_done[t * 2 + h]);
+                if (h == 1) umma_commit_pred(leader, &v_empty[st]);
+                if (j + 1 == total) umma_commit_pred(leader, &o_full[t]);
+                if (t == 0) GQA_FTRACE(1, j, 2);
             }
         }
     } else {
@@ -232,98 +234,118 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             const uint32_t tS = tmem + lane_addr + (t == 0 ? Cfg::kColS0 : Cfg::kColS1);
             const uint32_t tO = tmem + lane_addr + (t == 0 ? Cfg::kColO0 : Cfg::kColO1);
             const float c = p.scale_log2;
-            const int n_mine = n_blk[t];
+            const uint64_t c2 = pack_f32x2(c, c);
+            const int total = 2 * n_blk[t];
             const int diag_block = (q0 + t * kTile) / kTile;  // only this block needs the causal mask
             float m_run = -INFINITY;  // running maximum of the raw logits that P is measured against
             float l_run = 0.f;
             bool ok = true;
-            for (int n = 0; n < n_mine; ++n) {
-                ok = mbar_wait(&s_full[t], n & 1, ctx, 30);
+            for (int j = 0; j < total; ++j) {
+                const int n = j >> 1, h = j & 1;
+                ok = mbar_wait(&s_full[t * 2 + h], n & 1, ctx, 30);
                 if (!ok) break;
                 tc_fence_after_sync();
-                if (warp == 0) GQA_FTRACE(0, n, 0);
-                if (warp == 4) GQA_FTRACE(2, n, 0);
+                if (warp == 0) GQA_FTRACE(0, j, 0);
+                if (warp == 4) GQA_FTRACE(2, j, 0);
+                if (t == 0) GQA_FTRACE(4, j, warp & 3);
                 const bool masked = p.causal && (n == diag_block);
-                // the whole 128-column row of S into registers (one TMEM round trip), then the row maximum
-                // with four independent partial maxima (a single chain of 128 dependent max ops is slow)
-                uint32_t v[128];
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) tmem_ld32p(tS + ch * 32, v + ch * 32);
+                const int col0 = h * kHalf;  // column of v[0] inside the 128-key block
+                // the 64-column half row of S into registers (one TMEM round trip), then the row maximum with
+                // four independent chains of three-input maxima
+                uint32_t v[kHalf];
+                tmem_ld32p(tS + col0, v);
+                tmem_ld32p(tS + col0 + 32, v + 32);
                 tmem_wait_ld();
                 float mx;
                 {
                     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     if (masked) {
 #pragma unroll
-                        for (int i = 0; i < 128; ++i)
-                            m4[i & 3] = (i > r) ? m4[i & 3] : fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                        for (int i = 0; i < kHalf; ++i)
+                            m4[i & 3] = (col0 + i > r) ? m4[i & 3] : fmaxf(m4[i & 3], __uint_as_float(v[i]));
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 128; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                        for (int i = 0; i < kHalf; i += 2)
+                            m4[(i >> 1) & 3] = max3_f32(m4[(i >> 1) & 3], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
                     }
                     mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
                 }
-                if (warp == 0) GQA_FTRACE(0, n, 1);
+                if (warp == 0) GQA_FTRACE(0, j, 1);
                 const float m_new = fmaxf(m_run, mx);
-                const bool grow = (m_new - m_run) * c > kRescaleThreshold;  // true on the first block (m_run = -inf)
+                const bool grow = (m_new - m_run) * c > kRescaleThreshold;  // true on the first half-block (m_run = -inf)
                 if (__any_sync(0xffffffffu, grow)) {
                     const float m_next = grow ? m_new : m_run;
                     const float alpha = ex2_approx((m_run - m_next) * c);
                     l_run *= alpha;
                     m_run = m_next;
-                    if (n > 0) {
+                    if (j > 0) {
+                        // O holds P(0..j-1) V; the last of those products may still be running
+                        ok = mbar_wait(&pv_done[t * 2 + (h ^ 1)], ((j - 1) >> 1) & 1, ctx, 32);
+                        if (!ok) break;
+                        tc_fence_after_sync();
 #pragma unroll 1
                         for (int ch = 0; ch < D / 32; ++ch) {
-                            uint32_t v[32];
-                            tmem_ld32(tO + ch * 32, v);
+                            uint32_t w[32];
+                            tmem_ld32(tO + ch * 32, w);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                            tmem_st32(tO + ch * 32, v);
+                            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * alpha);
+                            tmem_st32(tO + ch * 32, w);
                         }
                     }
                 }
-                // The exp unit is the shared bottleneck, so the two tiles are kept out of phase: one tile's exps
-                // then overlap the other tile's tensor-core round trip instead of both idling together.
-                // D = 128 (tensor and exp work balanced): strict turns 0,1,0,1,... in the exp phase.
-                // D = 64 (exp-bound): only the first exp phase of tile 1 is delayed until tile 0 finished its own;
-                // measured, strict turns cost 5 % there and gain 25 % at D = 128.
-                if constexpr (D == 128) {
-                    if (t == 1) {
-                        if (n < n_blk[0]) ok = mbar_wait(&turn[0], n & 1, ctx, 35);
-                    } else if (n > 0 && n - 1 < n_blk[1]) {
-                        ok = mbar_wait(&turn[1], (n - 1) & 1, ctx, 36);
-                    }
-                } else {
-                    if (t == 1 && n == 0 && n_blk[0] > 0) ok = mbar_wait(&turn[0], 0, ctx, 35);
-                }
-                if (!ok) break;
-                // P = exp2(c*s - c*m), row sum (four partial sums), packed bf16 back into the first 64 S columns
+                // P = exp2(c*s - c*m) (packed fma), row sum (two packed partial sums), packed bf16 into the first
+                // 32 columns of this S buffer
                 const float mc = m_run * c;
-                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                float l_add;
+                if (!masked) {
+                    const uint64_t nmc2 = pack_f32x2(-mc, -mc);
+                    uint64_t l2[2] = {0ull, 0ull};
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t pk[16];
+                    for (int ch = 0; ch < 2; ++ch) {
+                        uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float e0 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i]), c, -mc));
-                        float e1 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i + 1]), c, -mc));
-                        if (masked) {
-                            if (ch * 32 + 2 * i > r) e0 = 0.f;
-                            if (ch * 32 + 2 * i + 1 > r) e1 = 0.f;
+                        for (int i = 0; i < 16; ++i) {
+                            const uint64_t x = fma_f32x2(
+                                pack_f32x2(__uint_as_float(v[ch * 32 + 2 * i]), __uint_as_float(v[ch * 32 + 2 * i + 1])), c2, nmc2);
+                            float x0, x1;
+                            unpack_f32x2(x, x0, x1);
+                            const float e0 = ex2_approx(x0), e1 = ex2_approx(x1);
+                            l2[i & 1] = add_f32x2(l2[i & 1], pack_f32x2(e0, e1));
+                            pk[i] = pack_bf16x2(e0, e1);
                         }
-                        l4[i & 3] += e0 + e1;
-                        pk[i] = pack_bf16x2(e0, e1);
+                        tmem_st16(tS + col0 + ch * 16, pk);
                     }
-                    tmem_st16(tS + ch * 16, pk);
+                    float a0, a1, b0, b1;
+                    unpack_f32x2(l2[0], a0, a1);
+                    unpack_f32x2(l2[1], b0, b1);
+                    l_add = (a0 + a1) + (b0 + b1);
+                } else {
+                    float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int ch = 0; ch < 2; ++ch) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int cc = col0 + ch * 32 + 2 * i;
+                            float e0 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i]), c, -mc));
+                            float e1 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i + 1]), c, -mc));
+                            if (cc > r) e0 = 0.f;
+                            if (cc + 1 > r) e1 = 0.f;
+                            l4[i & 3] += e0 + e1;
+                            pk[i] = pack_bf16x2(e0, e1);
+                        }
+                        tmem_st16(tS + col0 + ch * 16, pk);
+                    }
+                    l_add = (l4[0] + l4[1]) + (l4[2] + l4[3]);
                 }
-                l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-                if (D == 128 || (t == 0 && n == 0)) mbar_arrive(&turn[t]);
+                l_run += l_add;
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(&p_full[t]);
-                if (warp == 0) GQA_FTRACE(0, n, 2);
-                if (warp == 4) GQA_FTRACE(2, n, 2);
+                mbar_arrive(&p_full[t * 2 + h]);
+                if (warp == 0) GQA_FTRACE(0, j, 2);
+                if (warp == 4) GQA_FTRACE(2, j, 2);
+                GQA_FTRACE(t == 0 ? 3 : 5, j, warp & 3);
             }
             // epilogue: O / l -> bf16, LSE
             if (ok) ok = mbar_wait(&o_full[t], 0, ctx, 31);
@@ -355,7 +377,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // ---- teardown ---------------------------------------------------------------
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == kWarpQK) {
+    if (warp == kWarpMma0) {
         if (*abort_flag != 0) __nanosleep(20000);  // let in-flight copies and MMAs drain before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
