@@ -68,7 +68,8 @@ namespace {
 // Shared body of gqa_bwd and gqa_bwd_stage_times; `ev` is null or four events recorded around the stages.
 int run_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE, void* dQ,
             void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale, void* workspace,
-            size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev) {
+            size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev, unsigned int flags = 0) {
+    if (flags & ~(unsigned)GQA_BWD_DETERMINISTIC) return GQA_ERR_BAD_ARGUMENT;
     if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
@@ -89,6 +90,11 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
     void* lse_cols = w + ws.lse_cols_off;
     void* delta_cols = w + ws.delta_cols_off;
     float* dq_accum = reinterpret_cast<float*>(w + ws.dq_accum_off);
+    unsigned int* dq_turn = nullptr;
+    if (flags & GQA_BWD_DETERMINISTIC) {
+        dq_turn = reinterpret_cast<unsigned int*>(w + ws.dq_turn_off);
+        GQA_CUDA_TRY(cudaMemsetAsync(dq_turn, 0, ws.dq_turn_bytes, stream));
+    }
 
     GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, stream));
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[0], stream));
@@ -96,7 +102,7 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
                                     stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[1], stream));
-    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dK, dV, s, status, stream);
+    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[2], stream));
     rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream);
@@ -112,6 +118,13 @@ extern "C" int gqa_bwd(const void* Q, const void* K, const void* V, const void* 
                        void* workspace, size_t workspace_bytes, gqa_stream_t stream) {
     return run_bwd(Q, K, V, O, dO, LSE, dQ, dK, dV, B, Hq, Hkv, S, D, causal, scale, workspace, workspace_bytes,
                    reinterpret_cast<cudaStream_t>(stream), nullptr);
+}
+
+extern "C" int gqa_bwd_ex(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE,
+                          void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+                          void* workspace, size_t workspace_bytes, gqa_stream_t stream, unsigned int flags) {
+    return run_bwd(Q, K, V, O, dO, LSE, dQ, dK, dV, B, Hq, Hkv, S, D, causal, scale, workspace, workspace_bytes,
+                   reinterpret_cast<cudaStream_t>(stream), nullptr, flags);
 }
 
 extern "C" int gqa_bwd_stage_times(const void* Q, const void* K, const void* V, const void* O, const void* dO,

@@ -6,7 +6,7 @@
 // the command line, prints one JSON line per run and can drive several GPUs:
 //
 //   gqa_bench B Hq Hkv [S=4096] [D=64] [causal=0] [--data DIR] [--synthetic] [--iters N] [--warmup N]
-//             [--runs N] [--gpus N]
+//             [--runs N] [--gpus N] [--deterministic]
 //
 // With --gpus N the (batch x KV-head) groups are cut into N contiguous ranges, one host thread per
 // device runs the unmodified single-GPU entry points on its range (a range is itself a GQA problem with
@@ -37,6 +37,7 @@ struct Options {
     int B = 8, Hq = 12, Hkv = 4, S = 4096, D = 64, causal = 0;
     int iters = 100, warmup = 10, runs = 3, gpus = 1;
     bool synthetic = false;
+    bool deterministic = false;  // gqa_bwd_ex with GQA_BWD_DETERMINISTIC (ordered dQ reductions)
     std::string data = "data";
 };
 
@@ -121,7 +122,8 @@ void run_shard(int dev, const Options& o, const HostData& h, int g0, int g1, int
     CKR(cudaMalloc(&ws, ws_bytes));
     auto fwd = [&]() { return gqa_fwd(q, k, v, out, lse, Bs, Hqs, Hkvs, S, D, o.causal, scale, nullptr); };
     auto bwd = [&]() {
-        return gqa_bwd(q, k, v, out, d_o, lse, dq, dk, dv, Bs, Hqs, Hkvs, S, D, o.causal, scale, ws, ws_bytes, nullptr);
+        return gqa_bwd_ex(q, k, v, out, d_o, lse, dq, dk, dv, Bs, Hqs, Hkvs, S, D, o.causal, scale, ws, ws_bytes, nullptr,
+                          o.deterministic ? GQA_BWD_DETERMINISTIC : 0u);
     };
     GQR(fwd());
     GQR(gqa_check_status(nullptr, nullptr));
@@ -204,6 +206,7 @@ int main(int argc, char** argv) {
         std::string a = argv[i];
         if (a == "--data" && i + 1 < argc) o.data = argv[++i];
         else if (a == "--synthetic") o.synthetic = true;
+        else if (a == "--deterministic") o.deterministic = true;
         else if (a == "--iters" && i + 1 < argc) o.iters = std::atoi(argv[++i]);
         else if (a == "--warmup" && i + 1 < argc) o.warmup = std::atoi(argv[++i]);
         else if (a == "--runs" && i + 1 < argc) o.runs = std::atoi(argv[++i]);

@@ -118,6 +118,7 @@ struct BwdParams {
     __nv_bfloat16* dK;
     __nv_bfloat16* dV;
     unsigned int* status;
+    unsigned int* dq_turn;  // deterministic mode: one counter per 32 query rows (zeroed), else nullptr
     int Hq, Hkv, S, causal, n_tiles, G;
     float scale, scale_log2;
 };
@@ -394,28 +395,62 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         constexpr int kWarpStage = Cfg::kDqBoxes * 4096;
         uint8_t* stage = sDQ + warp * kWarpStage + lane * 128;
         const int sw = lane & 7;
+        // Deterministic mode: the reductions into one 32-row slice of the accumulator are applied in KV-tile order.
+        // The CTA of KV tile kt waits until the slice's counter reads kt (its predecessors run or have run: they
+        // have smaller block indices), and hands on with kt + 1 once its own reductions have completed.
+        // Fill cost: CTA kt starts its first reduction kt hand-overs late; after that the stagger persists.
+        auto turn_acquire = [&](unsigned int* turn) -> bool {
+            uint32_t good = 1;
+            if (lane == 0) {
+                const long long t0 = clock64();
+                uint32_t polls = 0;
+                while (ld_acquire_gpu(turn) != (unsigned)kt) {
+                    if ((++polls & 0x3fu) == 0) {
+                        if (*abort_flag != 0) { good = 0; break; }
+                        if (clock64() - t0 > kWaitLimitCycles) {
+                            *abort_flag = 41;
+                            atomicCAS(p.status, 0u, 0x80000000u | (41u << 20) | (blockIdx.x & 0xfffffu));
+                            good = 0;
+                            break;
+                        }
+                    }
+                }
+                fence_proxy_async_all();  // the predecessor's reductions (async proxy) are ordered before ours
+            }
+            return __shfl_sync(0xffffffffu, good, 0) != 0;
+        };
+        auto turn_release = [&](unsigned int* turn) {
+            if (lane == 0) {
+                bulk_wait_all();  // our reductions have been applied
+                fence_proxy_async_all();
+                st_release_gpu(turn, (unsigned)kt + 1u);
+            }
+            __syncwarp();
+        };
         for (int it = 0; it < n_iter; ++it) {
             if (!mbar_wait(dq_full, it & 1, ctx, 40)) break;
             tc_fence_after_sync();
             GQA_TRACE(2, it, 0);
             const int row = q_row_of(it) + warp * 32;
+            unsigned int* turn = p.dq_turn ? p.dq_turn + (row >> 5) : nullptr;
+            bool turn_mine = (turn == nullptr);  // becomes true once this warp may reduce into the slice
             constexpr int kRounds = D / (32 * Cfg::kDqBoxes);
             if constexpr (Cfg::kDrainEarlyRelease) {
                 static_assert(!Cfg::kDrainEarlyRelease || (D == 128 && Cfg::kDqBoxes == 1), "four 32-column chunks, one box");
-                auto stage_and_reduce = [&](const uint32_t (&v)[32], int chunk) {
+                auto stage_box = [&](const uint32_t (&v)[32]) {
 #pragma unroll
                     for (int c8 = 0; c8 < 8; ++c8)
                         *reinterpret_cast<uint4*>(stage + ((c8 ^ sw) << 4)) =
                             make_uint4(v[4 * c8], v[4 * c8 + 1], v[4 * c8 + 2], v[4 * c8 + 3]);
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
+                };
+                auto reduce_box = [&](int chunk) {  // then wait until the box may be overwritten
+                    if (turn_mine && lane == 0) {
                         tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage, chunk * 32, row);
                         bulk_commit_group();
+                        bulk_wait_read_all();
                     }
-                };
-                auto wait_box_free = [&]() {
-                    if (lane == 0) bulk_wait_read_all();
                     __syncwarp();
                 };
                 uint32_t va[32], vb[32], vc[32];
@@ -423,18 +458,20 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 tmem_ld32(tDQ + 32, vb);
                 tmem_ld32(tDQ + 64, vc);
                 tmem_wait_ld();
-                stage_and_reduce(va, 0);
+                stage_box(va);
                 tmem_ld32(tDQ + 96, va);  // chunk 0 is in shared memory: its registers take chunk 3
                 tmem_wait_ld();
                 tc_fence_before_sync();
                 mbar_arrive(dq_empty);     // the dP^T columns are free after two TMEM round trips
-                wait_box_free();
-                stage_and_reduce(vb, 1);
-                wait_box_free();
-                stage_and_reduce(vc, 2);
-                wait_box_free();
-                stage_and_reduce(va, 3);
-                wait_box_free();
+                if (!turn_mine) turn_mine = turn_acquire(turn);
+                reduce_box(0);
+                stage_box(vb);
+                reduce_box(1);
+                stage_box(vc);
+                reduce_box(2);
+                stage_box(va);
+                reduce_box(3);
+                if (turn && turn_mine) turn_release(turn);
             } else {
     #pragma unroll 1
                 for (int rnd = 0; rnd < kRounds; ++rnd) {
@@ -454,7 +491,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
+                    if (!turn_mine) turn_mine = turn_acquire(turn);
+                    if (turn_mine && lane == 0) {
     #pragma unroll
                         for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)
                             tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage + bx * 4096, (rnd * Cfg::kDqBoxes + bx) * 32, row);
@@ -463,7 +501,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     }
                     __syncwarp();
                 }
+                if (turn && turn_mine) turn_release(turn);
             }
+            if (!turn_mine) break;  // a bounded wait gave up: the abort flag is set
             GQA_TRACE(2, it, 1);
         }
         if (lane == 0) bulk_wait_all();
@@ -648,7 +688,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 
 template <int D>
 int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
-                 const void* delta_cols, float* dq_accum, void* dK, void* dV, const Shape& s, unsigned int* status, cudaStream_t stream) {
+                 const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV, const Shape& s,
+                 unsigned int* status, cudaStream_t stream) {
     using Cfg = BwdCfg<D>;
     CUtensorMap mq, mk, mv, mdo;
     int rc = make_panel_tmap(&mq, Q, s.q_rows(), D, kTile);
@@ -674,6 +715,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.dK = static_cast<__nv_bfloat16*>(dK);
     p.dV = static_cast<__nv_bfloat16*>(dV);
     p.status = status;
+    p.dq_turn = dq_turn;
     p.Hq = s.Hq;
     p.Hkv = s.Hkv;
     p.S = s.S;
@@ -698,10 +740,11 @@ extern "C" int gqa_debug_copy_bwd_trace(long long* host) {
 #endif
 
 int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
-                          const void* delta_cols, float* dq_accum, void* dK, void* dV, const Shape& s,
-                          unsigned int* status, cudaStream_t stream) {
-    if (s.D == 64) return launch_bwd_t<64>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dK, dV, s, status, stream);
-    return launch_bwd_t<128>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dK, dV, s, status, stream);
+                          const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV,
+                          const Shape& s, unsigned int* status, cudaStream_t stream) {
+    if (s.D == 64)
+        return launch_bwd_t<64>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
+    return launch_bwd_t<128>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
 }
 
 }  // namespace gqa

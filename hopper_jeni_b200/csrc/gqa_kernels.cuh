@@ -18,13 +18,16 @@ struct Shape {
 struct BwdWorkspace {
     // lse_cols / delta_cols: per query row eight bf16 (16 bytes): a three-way bf16 split of -LSE/scale and of
     // -Delta in the first three, zeros after; they enter the S^T and dP^T products as one extra K step.
-    size_t status_off, lse_cols_off, delta_cols_off, dq_accum_off, total;
+    // dq_turn: one counter per 32 query rows, used only by the deterministic mode (order of the dQ reductions).
+    size_t status_off, lse_cols_off, delta_cols_off, dq_turn_off, dq_turn_bytes, dq_accum_off, total;
     explicit BwdWorkspace(const Shape& s) {
         auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
         status_off = 0;
         lse_cols_off = 256;
         delta_cols_off = lse_cols_off + up(s.q_rows() * 16);
-        dq_accum_off = delta_cols_off + up(s.q_rows() * 16);
+        dq_turn_off = delta_cols_off + up(s.q_rows() * 16);
+        dq_turn_bytes = s.q_rows() / 32 * sizeof(unsigned int);
+        dq_accum_off = dq_turn_off + up(dq_turn_bytes);
         total = dq_accum_off + up(s.q_rows() * (size_t)s.D * sizeof(float));
     }
 };
@@ -42,9 +45,11 @@ int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float
                      unsigned int* status, cudaStream_t stream);
 // Stage 2 of the backward: KV-tile-parallel main kernel (tcgen05 + TMEM + TMA); dK/dV written
 // once per element, dQ accumulated into dq_accum with fp32 reductions.
+// With dq_turn (zeroed counters, one per 32 query rows) the reductions of every dQ tile are applied in KV-tile
+// order, which makes dQ bit-reproducible; nullptr = unordered.
 int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
-                          const void* delta_cols, float* dq_accum, void* dK, void* dV, const Shape& s,
-                          unsigned int* status, cudaStream_t stream);
+                          const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV,
+                          const Shape& s, unsigned int* status, cudaStream_t stream);
 
 // CUDA-core checker kernels (slow, simple; fp32 math on bf16 inputs).
 int launch_fwd_simt(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,

@@ -135,6 +135,18 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 // Wait until all committed bulk groups have completed.
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Ordering between the generic proxy (ordinary loads/stores) and the async proxy (TMA), all state spaces.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Device-scope flag in global memory.
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // ----------------------------------------------------------------------------
 // TMEM allocation (one warp, all 32 lanes; columns: power of two, 32..512)
 // ----------------------------------------------------------------------------

@@ -63,8 +63,9 @@ def bwd_workspace_bytes(B, Hq, Hkv, S, D, causal=False) -> int:
 
 
 def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None = None,
-                 workspace=None, dq=None, dk=None, dv=None, stream=None):
-    """dQ, dK, dV.  Mirrors ``launch_gqa_backward_vj1d`` (G derived from the head counts)."""
+                 workspace=None, dq=None, dk=None, dv=None, stream=None, deterministic: bool = False):
+    """dQ, dK, dV.  Mirrors ``launch_gqa_backward_vj1d`` (G derived from the head counts).
+    ``deterministic`` orders the dQ reductions (``GQA_BWD_DETERMINISTIC``): bit-reproducible dQ, slower."""
     lib = capi.load_library()
     for t, n in ((q, "Q"), (k, "K"), (v, "V"), (o, "O"), (do, "dO")):
         _req(t, n, torch.bfloat16)
@@ -80,10 +81,14 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
     with torch.cuda.device(q.device):
-        rc = lib.gqa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
-                         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,
-                         workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream_ptr(stream))
-    capi.check("gqa_bwd", rc)
+        args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,
+                workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream_ptr(stream))
+        if deterministic:
+            rc = lib.gqa_bwd_ex(*args, capi.GQA_BWD_DETERMINISTIC)
+        else:
+            rc = lib.gqa_bwd(*args)
+    capi.check("gqa_bwd_ex" if deterministic else "gqa_bwd", rc)
     return dq, dk, dv
 
 

@@ -77,6 +77,23 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
             void* workspace, size_t workspace_bytes, gqa_stream_t stream);
 
 /*
+ * gqa_bwd with option flags.  flags = 0 is gqa_bwd.
+ * GQA_BWD_DETERMINISTIC: the fp32 reductions into every 32-row slice of the dQ accumulator are applied in
+ * KV-tile order (a counter per slice in the workspace hands the turn from one thread block to the next), so dQ
+ * is bit-reproducible from run to run as dK and dV always are.  The reference's dQ path is order-dependent
+ * (cp.reduce.async.bulk add, src/attention/GQA_bwd_baseline.cu:360-365, run-to-run differences noted in
+ * docs/report.md:115-116) and has no such switch; its determinism probe
+ * (src/attention/vj1d_determinism_probe.cu:33) is what this mode is checked with.  Slower than the default
+ * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.
+ * Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
+ */
+#define GQA_BWD_DETERMINISTIC 1u
+int gqa_bwd_ex(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+               const float* LSE, void* dQ, void* dK, void* dV,
+               int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+               void* workspace, size_t workspace_bytes, gqa_stream_t stream, unsigned int flags);
+
+/*
  * Backward for callers that cannot allocate device memory.  No counterpart in the
  * reference (its launcher grows function-static cudaMalloc buffers on demand).
  *
