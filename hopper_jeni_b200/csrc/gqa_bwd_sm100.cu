@@ -44,10 +44,13 @@ using namespace sm100;
 
 // Optional timeline tracing (development builds only): block 0 stamps clock64 at a few points per iteration.
 #ifdef GQA_BWD_TRACE
+#ifndef GQA_BWD_TRACE_BLOCK
+#define GQA_BWD_TRACE_BLOCK 0
+#endif
 __device__ long long g_bwd_trace[3][64][4];
 #define GQA_TRACE(role, it, slot)                                                                  \
     do {                                                                                           \
-        if (blockIdx.x == 0 && (it) < 64 && (threadIdx.x & 31) == 0) g_bwd_trace[role][it][slot] = clock64(); \
+        if (blockIdx.x == GQA_BWD_TRACE_BLOCK && (it) < 64 && (threadIdx.x & 31) == 0) g_bwd_trace[role][it][slot] = clock64(); \
     } while (0)
 #else
 #define GQA_TRACE(role, it, slot) \
@@ -71,7 +74,11 @@ struct BwdCfg {
     static constexpr int kHalves = kCols / 16;            // 16-column steps per thread and stage
     static constexpr int kEwThreads = kEwGroups * 128;
     // D = 128: dK and dQ (both wait for dS^T) are issued by one warp, which makes the CTA exactly 16 warps.
+#ifdef GQA_BWD_MERGE64
+    static constexpr bool kMergeDkDq = true;
+#else
     static constexpr bool kMergeDkDq = (D == 128);
+#endif
     static constexpr int kWarpTma = kWarpEw0 + 4 * kEwGroups, kWarpMmaS = kWarpTma + 1, kWarpMmaDV = kWarpTma + 2,
                          kWarpMmaDK = kWarpTma + 3, kWarpMmaDQ = kMergeDkDq ? kWarpMmaDK : kWarpTma + 4;
     static constexpr int kThreads = (kWarpMmaDQ + 1) * 32;
@@ -182,8 +189,11 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // +6.7 % at the headline shape).  Causal: the KV tile is the slow index so the longest items start first
     // (load balance matters more there: measured +6 %). ----
     const int groups = gridDim.x / p.n_tiles;  // B * Hkv
-    const int kt = p.causal ? (int)blockIdx.x / groups : (int)blockIdx.x % p.n_tiles;
-    const int grp = p.causal ? (int)blockIdx.x % groups : (int)blockIdx.x / p.n_tiles;
+    // The deterministic mode also takes the KV tile as the slow index: the CTAs of one group that run at the same
+    // time must reduce one after the other, and this order keeps only a few of them in flight together.
+    const bool kt_major = p.causal || p.dq_turn != nullptr;
+    const int kt = kt_major ? (int)blockIdx.x / groups : (int)blockIdx.x % p.n_tiles;
+    const int grp = kt_major ? (int)blockIdx.x % groups : (int)blockIdx.x / p.n_tiles;
     const int b = grp / p.Hkv, hkv = grp % p.Hkv;
     const int qt0 = p.causal ? kt : 0;
     const int n_qt = p.n_tiles - qt0;
@@ -399,12 +409,12 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // The CTA of KV tile kt waits until the slice's counter reads kt (its predecessors run or have run: they
         // have smaller block indices), and hands on with kt + 1 once its own reductions have completed.
         // Fill cost: CTA kt starts its first reduction kt hand-overs late; after that the stagger persists.
-        auto turn_acquire = [&](unsigned int* turn) -> bool {
+        auto turn_acquire = [&](unsigned int* turn, unsigned int early) -> bool {
             uint32_t good = 1;
             if (lane == 0) {
                 const long long t0 = clock64();
                 uint32_t polls = 0;
-                while (ld_acquire_gpu(turn) != (unsigned)kt) {
+                while (early != (unsigned)kt && ld_acquire_gpu(turn) != (unsigned)kt) {
                     if ((++polls & 0x3fu) == 0) {
                         if (*abort_flag != 0) { good = 0; break; }
                         if (clock64() - t0 > kWaitLimitCycles) {
@@ -415,25 +425,34 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                         }
                     }
                 }
-                fence_proxy_async_all();  // the predecessor's reductions (async proxy) are ordered before ours
+                fence_proxy_async_global();  // our reductions (async proxy) are ordered after the acquire
             }
             return __shfl_sync(0xffffffffu, good, 0) != 0;
         };
-        auto turn_release = [&](unsigned int* turn) {
-            if (lane == 0) {
-                bulk_wait_all();  // our reductions have been applied
-                fence_proxy_async_all();
-                st_release_gpu(turn, (unsigned)kt + 1u);
+        // The turn of a tile is handed on one iteration later, just before the next tile's reductions are issued:
+        // by then the reductions have had a TMEM round trip and a staging pass to land, so the wait for their
+        // completion is short.  (Holding the turns of three tiles instead was slower: the hand-over delay, not the
+        // wait, is what the CTAs of a group queue on.)
+        unsigned int* held = nullptr;  // slice whose turn this warp still holds
+        auto release_held = [&]() {
+            if (held) {
+                if (lane == 0) {
+                    bulk_wait_all();  // completed: the sums are visible to this thread
+                    st_release_gpu(held, (unsigned)kt + 1u);
+                }
+                __syncwarp();
+                held = nullptr;
             }
-            __syncwarp();
         };
         for (int it = 0; it < n_iter; ++it) {
-            if (!mbar_wait(dq_full, it & 1, ctx, 40)) break;
-            tc_fence_after_sync();
-            GQA_TRACE(2, it, 0);
             const int row = q_row_of(it) + warp * 32;
             unsigned int* turn = p.dq_turn ? p.dq_turn + (row >> 5) : nullptr;
             bool turn_mine = (turn == nullptr);  // becomes true once this warp may reduce into the slice
+            // first look at the counter now: its round trip to L2 hides behind the TMEM loads and the staging
+            const unsigned int early = (turn && lane == 0) ? ld_acquire_gpu(turn) : 0xffffffffu;
+            if (!mbar_wait(dq_full, it & 1, ctx, 40)) break;
+            tc_fence_after_sync();
+            GQA_TRACE(2, it, 0);
             constexpr int kRounds = D / (32 * Cfg::kDqBoxes);
             if constexpr (Cfg::kDrainEarlyRelease) {
                 static_assert(!Cfg::kDrainEarlyRelease || (D == 128 && Cfg::kDqBoxes == 1), "four 32-column chunks, one box");
@@ -463,7 +482,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 tmem_wait_ld();
                 tc_fence_before_sync();
                 mbar_arrive(dq_empty);     // the dP^T columns are free after two TMEM round trips
-                if (!turn_mine) turn_mine = turn_acquire(turn);
+                release_held();
+                if (!turn_mine) turn_mine = turn_acquire(turn, early);
                 reduce_box(0);
                 stage_box(vb);
                 reduce_box(1);
@@ -471,7 +491,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 reduce_box(2);
                 stage_box(va);
                 reduce_box(3);
-                if (turn && turn_mine) turn_release(turn);
+                if (turn && turn_mine) held = turn;
             } else {
     #pragma unroll 1
                 for (int rnd = 0; rnd < kRounds; ++rnd) {
@@ -491,7 +511,10 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (!turn_mine) turn_mine = turn_acquire(turn);
+                    release_held();
+                    GQA_TRACE(2, it, 2);
+                    if (!turn_mine) turn_mine = turn_acquire(turn, early);
+                    GQA_TRACE(2, it, 3);
                     if (turn_mine && lane == 0) {
     #pragma unroll
                         for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)
@@ -501,11 +524,12 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     }
                     __syncwarp();
                 }
-                if (turn && turn_mine) turn_release(turn);
+                if (turn && turn_mine) held = turn;
             }
             if (!turn_mine) break;  // a bounded wait gave up: the abort flag is set
             GQA_TRACE(2, it, 1);
         }
+        release_held();
         if (lane == 0) bulk_wait_all();
     } else if (warp < Cfg::kWarpTma) {
         // ======================= elementwise warpgroups (P^T and dS^T) =======================

@@ -135,8 +135,8 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 // Wait until all committed bulk groups have completed.
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// Ordering between the generic proxy (ordinary loads/stores) and the async proxy (TMA), all state spaces.
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Ordering between the generic proxy (ordinary loads/stores) and the async proxy (TMA) for global memory.
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 // Device-scope flag in global memory.
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
     unsigned int v;
