@@ -13,6 +13,7 @@ _LIB = None
 
 GQA_OK = 0
 GQA_BWD_DETERMINISTIC = 1
+GQA_LAYOUT_BSHD = 2
 STATUS_NAMES = {
     0: "GQA_OK", -1: "GQA_ERR_BAD_ARGUMENT", -2: "GQA_ERR_UNSUPPORTED", -3: "GQA_ERR_WORKSPACE",
     -4: "GQA_ERR_CUDA", -5: "GQA_ERR_DEVICE_TIMEOUT", -6: "GQA_ERR_ARCH",
@@ -23,6 +24,7 @@ _vp, _fp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c
 #: symbol -> (restype, argtypes); one entry per declaration in include/gqa.h
 EXPORTS = {
     "gqa_fwd": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "gqa_fwd_ex": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp, ctypes.c_uint]),
     "launch_gqa": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "gqa_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),

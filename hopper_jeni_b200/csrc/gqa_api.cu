@@ -33,8 +33,11 @@ int check_shape(int B, int Hq, int Hkv, int S, int D) {
 
 }  // namespace
 
-extern "C" int gqa_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv, int S,
-                       int D, int causal, float scale, gqa_stream_t stream_) {
+namespace {
+
+int run_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv, int S, int D,
+            int causal, float scale, cudaStream_t stream, unsigned int flags) {
+    if (flags & ~(unsigned)GQA_LAYOUT_BSHD) return GQA_ERR_BAD_ARGUMENT;
     if (!Q || !K || !V || !O) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
@@ -43,12 +46,24 @@ extern "C" int gqa_fwd(const void* Q, const void* K, const void* V, void* O, flo
         return GQA_ERR_BAD_ARGUMENT;
     rc = check_device();
     if (rc) return rc;
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     unsigned int* status = nullptr;
     rc = gqa::forward_status_word(&status);
     if (rc) return rc;
-    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    s.bshd = (flags & GQA_LAYOUT_BSHD) ? 1 : 0;
     return gqa::launch_fwd_sm100(Q, K, V, O, LSE, s, status, stream);
+}
+
+}  // namespace
+
+extern "C" int gqa_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv, int S,
+                       int D, int causal, float scale, gqa_stream_t stream) {
+    return run_fwd(Q, K, V, O, LSE, B, Hq, Hkv, S, D, causal, scale, reinterpret_cast<cudaStream_t>(stream), 0u);
+}
+
+extern "C" int gqa_fwd_ex(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv,
+                          int S, int D, int causal, float scale, gqa_stream_t stream, unsigned int flags) {
+    return run_fwd(Q, K, V, O, LSE, B, Hq, Hkv, S, D, causal, scale, reinterpret_cast<cudaStream_t>(stream), flags);
 }
 
 extern "C" int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv,
@@ -69,14 +84,15 @@ namespace {
 int run_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE, void* dQ,
             void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale, void* workspace,
             size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev, unsigned int flags = 0) {
-    if (flags & ~(unsigned)GQA_BWD_DETERMINISTIC) return GQA_ERR_BAD_ARGUMENT;
+    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD)) return GQA_ERR_BAD_ARGUMENT;
     if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
     const void* ptrs[] = {Q, K, V, O, dO, LSE, dQ, dK, dV};
     for (const void* p : ptrs)
         if (!gqa::aligned16(p)) return GQA_ERR_BAD_ARGUMENT;
-    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
+    s.bshd = (flags & GQA_LAYOUT_BSHD) ? 1 : 0;
     const gqa::BwdWorkspace ws(s);
     if (!workspace || workspace_bytes < ws.total) {
         gqa::note_text("backward workspace: need %zu bytes, got %zu", ws.total, workspace ? workspace_bytes : (size_t)0);
@@ -99,13 +115,13 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
     GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, stream));
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[0], stream));
     rc = gqa::launch_bwd_preprocess(O, dO, LSE, 1.0f / scale, nullptr, lse_cols, delta_cols, dq_accum, s.q_rows(), D,
-                                    stream);
+                                    stream, s.bshd ? S : 0, s.bshd ? Hq : 0);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[1], stream));
     rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[2], stream));
-    rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream);
+    rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream, D, s.bshd ? S : 0, s.bshd ? Hq : 0);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[3], stream));
     return GQA_OK;

@@ -19,15 +19,16 @@
 //   dK  += dS^T Q      (A = dS^T K-major, B = Q panel read MN-major)
 //   dQ   = dS K        (A = dS^T read MN-major, B = K panel read MN-major)
 //
-// Roles at D = 64 (25 warps; D = 128 uses 16: two elementwise warpgroups, dK and dQ from one issuer):
+// Roles at D = 64 (24 warps; D = 128 uses 16: two elementwise warpgroups):
 //   warps 0-3    drain dQ tiles from TMEM into the fp32 accumulator
 //   warps 4-19   four elementwise warpgroups; each owns 32 query columns of the tile pair
 //   warp  20     TMA producer
-//   warps 21-24  UMMA issuers: [S^T, dP^T] | dV | dK | dQ
+//   warps 21-23  UMMA issuers: [S^T, dP^T] | dV | [dK, dQ]
 // The five GEMMs wait on different producers, and one issuing warp sustains a 128x64x16 product
 // only every 57 cycles (78 when A comes from TMEM) against 32 cycles of tensor math, so they are
-// issued by four warps in parallel, each a warp-uniform loop with one elected lane; mbarriers
-// carry every cross-warp dependency.
+// issued by three warps in parallel, each a warp-uniform loop with one elected lane; mbarriers
+// carry every cross-warp dependency.  Registers are granted in steps of four warps, so 24 warps
+// get 80 registers per thread where 25 got 72 (dK and dQ both wait for dS^T and share a warp).
 //
 // Replaces gqa_bwd_vj1d (src/attention/GQA_bwd_baseline.cu:405-547) in the
 // G-loop-inside-the-CTA form of gqa_bwd_vz2_wgmma (src/attention/GQA_bwd.cu:15207-15342);
@@ -73,15 +74,10 @@ struct BwdCfg {
     static constexpr int kCols = kTile / kEwGroups;       // query columns per elementwise thread
     static constexpr int kHalves = kCols / 16;            // 16-column steps per thread and stage
     static constexpr int kEwThreads = kEwGroups * 128;
-    // D = 128: dK and dQ (both wait for dS^T) are issued by one warp, which makes the CTA exactly 16 warps.
-#ifdef GQA_BWD_MERGE64
-    static constexpr bool kMergeDkDq = true;
-#else
-    static constexpr bool kMergeDkDq = (D == 128);
-#endif
+    // dK and dQ (both wait for dS^T) are issued by one warp, which makes the CTA 24 / 16 warps.
     static constexpr int kWarpTma = kWarpEw0 + 4 * kEwGroups, kWarpMmaS = kWarpTma + 1, kWarpMmaDV = kWarpTma + 2,
-                         kWarpMmaDK = kWarpTma + 3, kWarpMmaDQ = kMergeDkDq ? kWarpMmaDK : kWarpTma + 4;
-    static constexpr int kThreads = (kWarpMmaDQ + 1) * 32;
+                         kWarpMmaDK = kWarpTma + 3;
+    static constexpr int kThreads = (kWarpMmaDK + 1) * 32;
     // D = 128: dQ sits in the dP^T columns, so the next dP^T product waits for the drain.  The drain warps
     // therefore pull the tile into registers as fast as TMEM delivers it (three 32-column chunks at once, the
     // fourth as soon as the first is staged) and hand the columns back before the copy engine has taken anything.
@@ -126,7 +122,7 @@ struct BwdParams {
     __nv_bfloat16* dV;
     unsigned int* status;
     unsigned int* dq_turn;  // deterministic mode: one counter per 32 query rows (zeroed), else nullptr
-    int Hq, Hkv, S, causal, n_tiles, G;
+    int Hq, Hkv, S, causal, n_tiles, G, bshd;
     float scale, scale_log2;
 };
 
@@ -200,7 +196,12 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     const int n_iter = p.G * n_qt;
     const int kv_row0 = (b * p.Hkv + hkv) * p.S + kt * kTile;
     const int q_head0 = b * p.Hq + hkv * p.G;  // first query head of the group
-    auto q_row_of = [&](int it) { return (q_head0 + it / n_qt) * p.S + (qt0 + it % n_qt) * kTile; };
+    auto q_row_of = [&](int it) { return (q_head0 + it / n_qt) * p.S + (qt0 + it % n_qt) * kTile; };  // [B,Hq,S] order
+    // Tensor-map coordinates of the bf16 tiles.  [B,H,S,D] is a [B*H*S, D] matrix: x = 0, y = the flattened row;
+    // [B,S,H,D] is a [B*S, H*D] matrix: x = head * D, y = b * S + s.  The workspace arrays keep [B,Hq,S] order.
+    const int kv_x = p.bshd ? hkv * D : 0, kv_y = p.bshd ? b * p.S + kt * kTile : kv_row0;
+    auto q_x_of = [&](int it) { return p.bshd ? (hkv * p.G + it / n_qt) * D : 0; };
+    auto q_y_of = [&](int it) { return p.bshd ? b * p.S + (qt0 + it % n_qt) * kTile : q_row_of(it); };
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -252,11 +253,11 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tma_prefetch_desc(&mapDltCol);
             mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
             for (int pn = 0; pn < Cfg::kPanels; ++pn) {
-                tma_load_2d(sK + pn * kPanel, &mapK, kv_full, pn * 64, kv_row0);
-                tma_load_2d(sV + pn * kPanel, &mapV, kv_full, pn * 64, kv_row0);
+                tma_load_2d(sK + pn * kPanel, &mapK, kv_full, kv_x + pn * 64, kv_y);
+                tma_load_2d(sV + pn * kPanel, &mapV, kv_full, kv_x + pn * 64, kv_y);
             }
             for (int it = 0; it < n_iter; ++it) {
-                const int row = q_row_of(it);
+                const int row = q_row_of(it), qx = q_x_of(it), qy = q_y_of(it);
                 {
                     const int st = it % Cfg::kQStages;
                     const uint32_t use = it / Cfg::kQStages;
@@ -264,7 +265,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     // the -LSE/scale columns of the tile ride with Q (both are operands of S^T)
                     mbar_expect_tx(&q_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                        tma_load_2d(sQ + st * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[st], pn * 64, row);
+                        tma_load_2d(sQ + st * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[st], qx + pn * 64, qy);
                     tma_load_2d(sLseCol + st * Cfg::kColPanel, &mapLseCol, &q_full[st], 0, row);
                 }
                 {
@@ -274,7 +275,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     // the -Delta columns ride with dO (both are operands of dP^T)
                     mbar_expect_tx(&do_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                        tma_load_2d(sDO + st * Cfg::kTileBytes + pn * kPanel, &mapDO, &do_full[st], pn * 64, row);
+                        tma_load_2d(sDO + st * Cfg::kTileBytes + pn * kPanel, &mapDO, &do_full[st], qx + pn * 64, qy);
                     tma_load_2d(sDltCol + st * Cfg::kColPanel, &mapDltCol, &do_full[st], 0, row);
                 }
             }
@@ -342,10 +343,10 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
         if (ok) umma_commit_pred(leader, acc_full);
     } else if (warp == Cfg::kWarpMmaDK) {
-        // ======================= issuer: dK += dS^T Q(it)  (A = dS^T K-major, B = Q read MN-major) =======================
+        // ======================= issuer: dK += dS^T Q(it)  (A = dS^T K-major, B = Q read MN-major), then dQ(it) =======================
         const uint32_t leader = elect_one() ? 1u : 0u;
         const uint32_t idesc = make_idesc_bf16(128, D, false, true);
-        bool ok = Cfg::kMergeDkDq ? mbar_wait(kv_full, 0, ctx, 34) : true;
+        bool ok = mbar_wait(kv_full, 0, ctx, 34);
         for (int it = 0; it < n_iter && ok; ++it) {
             const int qs = it % Cfg::kQStages;
             ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 32) && mbar_wait(ds_ready, it & 1, ctx, 33);
@@ -364,7 +365,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             }
             umma_commit_pred(leader, ds_free);
             umma_commit_pred(leader, &q_empty[qs]);
-            if constexpr (Cfg::kMergeDkDq) {  // dQ(it) = dS K from the same warp
+            {  // dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major)
                 if (it > 0) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 36);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -379,24 +380,6 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             }
         }
         if (ok) umma_commit_pred(leader, acc_full);
-    } else if (!Cfg::kMergeDkDq && warp == Cfg::kWarpMmaDQ) {
-        // ======================= issuer: dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major) =======================
-        const uint32_t leader = elect_one() ? 1u : 0u;
-        const uint32_t idesc = make_idesc_bf16(128, D, true, true);
-        bool ok = mbar_wait(kv_full, 0, ctx, 34);
-        for (int it = 0; it < n_iter && ok; ++it) {
-            ok = mbar_wait(ds_ready, it & 1, ctx, 35);
-            if (ok && it > 0) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 36);
-            if (!ok) break;
-            tc_fence_after_sync();
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-                umma_ss_pred(leader, tmem + Cfg::kColDQ, make_sdesc_sw128(ds_addr + kk * 2048, kPanel, 1024),
-                             make_sdesc_sw128(k_addr + kk * 2048, kPanel, 1024), idesc, kk > 0);
-            umma_commit_pred(leader, dq_full);
-            umma_commit_pred(leader, ds_free);
-            GQA_TRACE(1, it, 3);
-        }
     } else if (warp < kWarpEw0) {
         // ======================= dQ drain warps =======================
         // Each warp owns 32 query rows: TMEM -> registers -> its own swizzled staging boxes -> TMA reduce-add
@@ -676,11 +659,12 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (ok) {
             tc_fence_after_sync();
             constexpr int kQuarter = D / Cfg::kEwGroups;  // columns of dV / dK per warpgroup
-            const size_t grow = (size_t)kv_row0 + j;
+            // element offset of this key row in dK / dV
+            const size_t kv_elem = p.bshd ? ((size_t)(kv_y + j) * p.Hkv + hkv) * D : ((size_t)kv_row0 + j) * D;
 #pragma unroll 1
             for (int which = 0; which < 2; ++which) {
                 const uint32_t tA = tmem + lane_addr + (which == 0 ? Cfg::kColDV : Cfg::kColDK) + w * kQuarter;
-                __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + grow * D + w * kQuarter;
+                __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + kv_elem + w * kQuarter;
                 const float mul = which == 0 ? 1.0f : p.scale;
 #pragma unroll
                 for (int ch = 0; ch < kQuarter / 16; ++ch) {
@@ -716,13 +700,16 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
                  unsigned int* status, cudaStream_t stream) {
     using Cfg = BwdCfg<D>;
     CUtensorMap mq, mk, mv, mdo;
-    int rc = make_panel_tmap(&mq, Q, s.q_rows(), D, kTile);
+    // rows x columns of the matrix each bf16 tensor is (see the coordinates in the kernel)
+    const uint64_t q_r = s.bshd ? (uint64_t)s.B * s.S : s.q_rows(), q_c = s.bshd ? (uint64_t)s.Hq * D : D;
+    const uint64_t kv_r = s.bshd ? (uint64_t)s.B * s.S : s.kv_rows(), kv_c = s.bshd ? (uint64_t)s.Hkv * D : D;
+    int rc = make_panel_tmap(&mq, Q, q_r, q_c, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mk, K, s.kv_rows(), D, kTile);
+    rc = make_panel_tmap(&mk, K, kv_r, kv_c, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mv, V, s.kv_rows(), D, kTile);
+    rc = make_panel_tmap(&mv, V, kv_r, kv_c, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mdo, dO, s.q_rows(), D, kTile);
+    rc = make_panel_tmap(&mdo, dO, q_r, q_c, kTile);
     if (rc) return rc;
     CUtensorMap mdq;
     rc = make_f32_box_tmap(&mdq, dq_accum, s.q_rows(), D, 32);
@@ -744,6 +731,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.Hkv = s.Hkv;
     p.S = s.S;
     p.causal = s.causal;
+    p.bshd = s.bshd;
     p.n_tiles = s.S / kTile;
     p.G = s.G();
     p.scale = s.scale;

@@ -69,7 +69,7 @@ struct FwdParams {
     __nv_bfloat16* O;
     float* LSE;
     unsigned int* status;
-    int Hq, Hkv, S, causal, n_pairs;
+    int Hq, Hkv, S, causal, n_pairs, bshd;
     float scale_log2;  // scale * log2(e)
 };
 
@@ -115,8 +115,11 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     n_blk[0] = p.causal ? (q0 / kTile + 1) : n_blocks_all;
     n_blk[1] = (n_tiles == 2) ? (p.causal ? (q0 / kTile + 2) : n_blocks_all) : 0;
     const int n_max = n_blk[1] > n_blk[0] ? n_blk[1] : n_blk[0];
-    const int q_row0 = (b * p.Hq + hq) * p.S + q0;   // row in the flattened [B*Hq*S, D] view
-    const int kv_row0 = (b * p.Hkv + hkv) * p.S;
+    const int q_row0 = (b * p.Hq + hq) * p.S + q0;   // row in [B,Hq,S] order (LSE)
+    // Tensor-map coordinates of the tiles.  [B,H,S,D] is a [B*H*S, D] matrix: x = 0, y = the flattened row.
+    // [B,S,H,D] is a [B*S, H*D] matrix: x = head * D, y = b * S + s.
+    const int q_x = p.bshd ? hq * D : 0, q_y = p.bshd ? b * p.S + q0 : q_row0;
+    const int kv_x = p.bshd ? hkv * D : 0, kv_y = p.bshd ? b * p.S : (b * p.Hkv + hkv) * p.S;
 
     // ---- setup ------------------------------------------------------------------
     if (tid == 0) {
@@ -156,7 +159,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             for (int t = 0; t < n_tiles; ++t) {
                 mbar_expect_tx(&q_full[t], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_2d(sQ + t * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[t], pn * 64, q_row0 + t * kTile);
+                    tma_load_2d(sQ + t * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[t], q_x + pn * 64, q_y + t * kTile);
             }
             for (int n = 0; n < n_max; ++n) {
                 const int st = n % Cfg::kStages;
@@ -164,11 +167,11 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 if (use > 0 && !mbar_wait(&k_empty[st], (use - 1) & 1, ctx, 10)) break;
                 mbar_expect_tx(&k_full[st], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_2d(sK + st * Cfg::kTileBytes + pn * kPanel, &mapK, &k_full[st], pn * 64, kv_row0 + n * kTile);
+                    tma_load_2d(sK + st * Cfg::kTileBytes + pn * kPanel, &mapK, &k_full[st], kv_x + pn * 64, kv_y + n * kTile);
                 if (use > 0 && !mbar_wait(&v_empty[st], (use - 1) & 1, ctx, 11)) break;
                 mbar_expect_tx(&v_full[st], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_2d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], pn * 64, kv_row0 + n * kTile);
+                    tma_load_2d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], kv_x + pn * 64, kv_y + n * kTile);
             }
         }
     } else if (warp >= kWarpMma0) {
@@ -353,7 +356,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 tc_fence_after_sync();
                 const float inv_l = 1.0f / l_run;
                 const size_t grow_ = (size_t)q_row0 + t * kTile + r;
-                __nv_bfloat16* orow = p.O + grow_ * D;
+                __nv_bfloat16* orow = p.bshd ? p.O + ((size_t)(q_y + t * kTile + r) * p.Hq + hq) * D : p.O + grow_ * D;
 #pragma unroll 1
                 for (int ch = 0; ch < D / 32; ++ch) {
                     uint32_t v[32];
@@ -388,11 +391,13 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
                  cudaStream_t stream) {
     using Cfg = FwdCfg<D>;
     CUtensorMap mq, mk, mv;
-    int rc = make_panel_tmap(&mq, Q, s.q_rows(), D, kTile);
+    // rows x columns of the matrix each tensor is (see the coordinates in the kernel)
+    const uint64_t bs = (uint64_t)s.B * s.S;
+    int rc = s.bshd ? make_panel_tmap(&mq, Q, bs, (uint64_t)s.Hq * D, kTile) : make_panel_tmap(&mq, Q, s.q_rows(), D, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mk, K, s.kv_rows(), D, kTile);
+    rc = s.bshd ? make_panel_tmap(&mk, K, bs, (uint64_t)s.Hkv * D, kTile) : make_panel_tmap(&mk, K, s.kv_rows(), D, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mv, V, s.kv_rows(), D, kTile);
+    rc = s.bshd ? make_panel_tmap(&mv, V, bs, (uint64_t)s.Hkv * D, kTile) : make_panel_tmap(&mv, V, s.kv_rows(), D, kTile);
     if (rc) return rc;
     GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::kSmemTotal));
@@ -404,6 +409,7 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
     p.Hkv = s.Hkv;
     p.S = s.S;
     p.causal = s.causal;
+    p.bshd = s.bshd;
     p.n_pairs = (s.S + 2 * kTile - 1) / (2 * kTile);
     p.scale_log2 = s.scale * kLog2e;
     dim3 grid(p.n_pairs, s.Hq, s.B);

@@ -9,6 +9,9 @@ namespace gqa {
 struct Shape {
     int B, Hq, Hkv, S, D, causal;
     float scale;
+    // 0: Q,O,dO,dQ [B,Hq,S,D] and K,V,dK,dV [B,Hkv,S,D] (the reference's layout); 1: [B,S,H,D] for all of them.
+    // LSE and the workspace arrays are always in [B,Hq,S] row order.
+    int bshd = 0;
     int G() const { return Hq / Hkv; }
     size_t q_rows() const { return (size_t)B * Hq * S; }
     size_t kv_rows() const { return (size_t)B * Hkv * S; }
@@ -35,10 +38,13 @@ struct BwdWorkspace {
 // Stage 1 of the backward: Delta = rowsum(dO*O); with `delta` it is stored as fp32, with the column arrays
 // the bf16 splits of -LSE*inv_scale and -Delta are stored (16 bytes per row each) and, if given, the dQ
 // accumulator is zeroed.
+// `S_bshd` / `H_bshd`: 0 when O, dO are in [B,H,S,D] order, else S and Hq of the [B,S,H,D] layout they are in.
 int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float inv_scale, float* delta,
-                          void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream);
-// Stage 3 of the backward: dQ = bf16(scale * dq_accum).
-int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream);
+                          void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream,
+                          int S_bshd = 0, int H_bshd = 0);
+// Stage 3 of the backward: dQ = bf16(scale * dq_accum) (dQ in [B,S,H,D] order when S_bshd / H_bshd are given).
+int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream,
+                       int D = 0, int S_bshd = 0, int H_bshd = 0);
 
 // Tensor-core forward (tcgen05 + TMEM + TMA).
 int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,

@@ -28,7 +28,7 @@ template <int D>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO, const float* __restrict__ lse,
                       float inv_scale, float* __restrict__ delta, uint4* __restrict__ lse_cols,
-                      uint4* __restrict__ delta_cols, float4* __restrict__ dq_accum, size_t rows) {
+                      uint4* __restrict__ delta_cols, float4* __restrict__ dq_accum, size_t rows, int S_bshd, int H_bshd) {
     constexpr int kLanesPerRow = D / 8;
     constexpr int kRowsPerWarp = 32 / kLanesPerRow;
     const int lane = threadIdx.x & 31;
@@ -39,8 +39,14 @@ bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO,
         const size_t row = base + sub;
         float acc = 0.f;
         if (row < rows) {
-            const uint4 a = O[row * kLanesPerRow + part];
-            const uint4 b = dO[row * kLanesPerRow + part];
+            // `row` counts in [B,H,S] order (LSE, Delta, accumulator); O and dO may be stored [B,S,H,D]
+            size_t src = row;
+            if (S_bshd) {
+                const size_t s_ = row % S_bshd, bh = row / S_bshd;
+                src = ((bh / H_bshd) * S_bshd + s_) * H_bshd + bh % H_bshd;
+            }
+            const uint4 a = O[src * kLanesPerRow + part];
+            const uint4 b = dO[src * kLanesPerRow + part];
             const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -66,8 +72,11 @@ bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO,
     }
 }
 
+// n8 groups of eight elements; per8 = D / 8 groups per row.  The accumulator is in [B,H,S] row order, dQ may be
+// stored [B,S,H,D] (S_bshd, H_bshd non-zero).
 __global__ void __launch_bounds__(256)
-dq_finalise_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, size_t n8, float scale) {
+dq_finalise_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, size_t n8, float scale, int per8, int S_bshd,
+                   int H_bshd) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
         const float4 a = acc[2 * i], b = acc[2 * i + 1];
         __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * scale, a.y * scale);
@@ -79,7 +88,12 @@ dq_finalise_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, size_
         o.y = *reinterpret_cast<uint32_t*>(&p1);
         o.z = *reinterpret_cast<uint32_t*>(&p2);
         o.w = *reinterpret_cast<uint32_t*>(&p3);
-        dq[i] = o;
+        size_t dst = i;
+        if (S_bshd) {
+            const size_t row = i / per8, s_ = row % S_bshd, bh = row / S_bshd;
+            dst = (((bh / H_bshd) * S_bshd + s_) * H_bshd + bh % H_bshd) * per8 + i % per8;
+        }
+        dq[dst] = o;
     }
 }
 
@@ -97,29 +111,31 @@ int grid_for(size_t work_items, int per_block) {
 }  // namespace
 
 int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float inv_scale, float* delta,
-                          void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream) {
+                          void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream,
+                          int S_bshd, int H_bshd) {
     const int rows_per_block = (256 / 32) * (256 / D);
     const int grid = grid_for(rows, rows_per_block);
     if (D == 64)
         bwd_preprocess_kernel<64><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
                                                             lse, inv_scale, delta, static_cast<uint4*>(lse_cols),
                                                             static_cast<uint4*>(delta_cols),
-                                                            reinterpret_cast<float4*>(dq_accum), rows);
+                                                            reinterpret_cast<float4*>(dq_accum), rows, S_bshd, H_bshd);
     else
         bwd_preprocess_kernel<128><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
                                                              lse, inv_scale, delta, static_cast<uint4*>(lse_cols),
                                                             static_cast<uint4*>(delta_cols),
-                                                            reinterpret_cast<float4*>(dq_accum), rows);
+                                                            reinterpret_cast<float4*>(dq_accum), rows, S_bshd, H_bshd);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;
 }
 
-int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream) {
+int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream, int D,
+                       int S_bshd, int H_bshd) {
     const size_t n8 = elems / 8;
     const int grid = grid_for(n8, 256);
     dq_finalise_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(dq_accum), static_cast<uint4*>(dQ), n8,
-                                                 scale);
+                                                 scale, D > 0 ? D / 8 : 1, D > 0 ? S_bshd : 0, H_bshd);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;

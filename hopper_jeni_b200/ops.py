@@ -28,7 +28,14 @@ def _req(t: torch.Tensor, name: str, dtype) -> None:
         raise ValueError(f"{name} must be contiguous")
 
 
-def _dims(q, k):
+def _dims(q, k, layout="bhsd"):
+    if layout == "bshd":
+        B, S, Hq, D = q.shape
+        if k.shape[0] != B or k.shape[1] != S or k.shape[3] != D:
+            raise ValueError(f"K/V shape {tuple(k.shape)} does not match Q {tuple(q.shape)}")
+        return B, Hq, k.shape[2], S, D
+    if layout != "bhsd":
+        raise ValueError(f"layout must be 'bhsd' or 'bshd', got {layout!r}")
     B, Hq, S, D = q.shape
     if k.shape[0] != B or k.shape[2] != S or k.shape[3] != D:
         raise ValueError(f"K/V shape {tuple(k.shape)} does not match Q {tuple(q.shape)}")
@@ -40,21 +47,24 @@ def launch_count() -> int:
     return int(capi.load_library().gqa_launch_count())
 
 
-def gqa_forward(q, k, v, causal: bool = False, scale: float | None = None, out=None, lse=None, stream=None):
-    """O, LSE = attention(Q, K, V).  Mirrors ``launch_gqa_v62`` with D and causal as arguments."""
+def gqa_forward(q, k, v, causal: bool = False, scale: float | None = None, out=None, lse=None, stream=None,
+                layout: str = "bhsd"):
+    """O, LSE = attention(Q, K, V).  Mirrors ``launch_gqa_v62`` with D and causal as arguments.
+    ``layout="bshd"``: Q, K, V, O are [B,S,H,D] (``GQA_LAYOUT_BSHD``); LSE is [B,Hq,S] either way."""
     lib = capi.load_library()
     for t, n in ((q, "Q"), (k, "K"), (v, "V")):
         _req(t, n, torch.bfloat16)
-    B, Hq, Hkv, S, D = _dims(q, k)
+    B, Hq, Hkv, S, D = _dims(q, k, layout)
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
     out = torch.empty_like(q) if out is None else out
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device) if lse is None else lse
     _req(out, "O", torch.bfloat16)
     _req(lse, "LSE", torch.float32)
     with torch.cuda.device(q.device):
-        rc = lib.gqa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                         B, Hq, Hkv, S, D, int(bool(causal)), scale, _stream_ptr(stream))
-    capi.check("gqa_fwd", rc)
+        rc = lib.gqa_fwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                            B, Hq, Hkv, S, D, int(bool(causal)), scale, _stream_ptr(stream),
+                            capi.GQA_LAYOUT_BSHD if layout == "bshd" else 0)
+    capi.check("gqa_fwd_ex", rc)
     return out, lse
 
 
@@ -63,14 +73,16 @@ def bwd_workspace_bytes(B, Hq, Hkv, S, D, causal=False) -> int:
 
 
 def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None = None,
-                 workspace=None, dq=None, dk=None, dv=None, stream=None, deterministic: bool = False):
+                 workspace=None, dq=None, dk=None, dv=None, stream=None, deterministic: bool = False,
+                 layout: str = "bhsd"):
     """dQ, dK, dV.  Mirrors ``launch_gqa_backward_vj1d`` (G derived from the head counts).
-    ``deterministic`` orders the dQ reductions (``GQA_BWD_DETERMINISTIC``): bit-reproducible dQ, slower."""
+    ``deterministic`` orders the dQ reductions (``GQA_BWD_DETERMINISTIC``): bit-reproducible dQ, slower.
+    ``layout="bshd"``: all bf16 tensors are [B,S,H,D] (``GQA_LAYOUT_BSHD``); LSE is [B,Hq,S] either way."""
     lib = capi.load_library()
     for t, n in ((q, "Q"), (k, "K"), (v, "V"), (o, "O"), (do, "dO")):
         _req(t, n, torch.bfloat16)
     _req(lse, "LSE", torch.float32)
-    B, Hq, Hkv, S, D = _dims(q, k)
+    B, Hq, Hkv, S, D = _dims(q, k, layout)
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
     need = bwd_workspace_bytes(B, Hq, Hkv, S, D, causal)
     if need == 0:
@@ -84,11 +96,9 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
         args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,
                 workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream_ptr(stream))
-        if deterministic:
-            rc = lib.gqa_bwd_ex(*args, capi.GQA_BWD_DETERMINISTIC)
-        else:
-            rc = lib.gqa_bwd(*args)
-    capi.check("gqa_bwd_ex" if deterministic else "gqa_bwd", rc)
+        flags = (capi.GQA_BWD_DETERMINISTIC if deterministic else 0) | (capi.GQA_LAYOUT_BSHD if layout == "bshd" else 0)
+        rc = lib.gqa_bwd_ex(*args, flags) if flags else lib.gqa_bwd(*args)
+    capi.check("gqa_bwd_ex" if flags else "gqa_bwd", rc)
     return dq, dk, dv
 
 

@@ -55,6 +55,18 @@ int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE,
                gqa_stream_t stream);
 
 /*
+ * gqa_fwd with option flags.  flags = 0 is gqa_fwd.
+ * GQA_LAYOUT_BSHD: Q and O are [B,S,Hq,D] and K and V [B,S,Hkv,D] (sequence-major, the layout the reference's
+ * harness hands to the FlashAttention and FlashInfer adapters, harness/competitors.py:116-122) instead of the
+ * canonical [B,H,S,D]; the tiles are fetched through tensor maps over the [B*S, H*D] matrix, so no transposed
+ * copy is made.  LSE stays [B,Hq,S].  Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
+ */
+#define GQA_LAYOUT_BSHD 2u
+int gqa_fwd_ex(const void* Q, const void* K, const void* V, void* O, float* LSE,
+               int B, int Hq, int Hkv, int S, int D, int causal, float scale,
+               gqa_stream_t stream, unsigned int flags);
+
+/*
 * Bytes of device scratch gqa_bwd needs for this shape (per-row LSE and Delta terms,
  * the fp32 dQ accumulator and a status word).  The reference keeps the same buffers as
  * function-static allocations inside its launcher
@@ -85,6 +97,7 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
  * docs/report.md:115-116) and has no such switch; its determinism probe
  * (src/attention/vj1d_determinism_probe.cu:33) is what this mode is checked with.  Slower than the default
  * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.
+ * GQA_LAYOUT_BSHD (see gqa_fwd_ex): Q, O, dO, dQ are [B,S,Hq,D] and K, V, dK, dV [B,S,Hkv,D]; LSE stays [B,Hq,S].
  * Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
  */
 #define GQA_BWD_DETERMINISTIC 1u
