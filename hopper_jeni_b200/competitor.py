@@ -28,8 +28,6 @@ from . import capi, ops
 def _supported(shape):
     if shape.D not in (64, 128):
         return False, f"D={shape.D} not supported (64 or 128)"
-    if shape.S % 128:
-        return False, f"S={shape.S} is not a multiple of 128"
     if shape.Hq % shape.Hkv:
         return False, "Hq is not a multiple of Hkv"
     if getattr(shape, "dtype", "bf16") != "bf16":

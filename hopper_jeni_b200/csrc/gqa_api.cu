@@ -26,7 +26,7 @@ int check_device() {
 int check_shape(int B, int Hq, int Hkv, int S, int D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0) return GQA_ERR_BAD_ARGUMENT;
     if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
-    if (S % 128 != 0 || Hq % Hkv != 0) return GQA_ERR_UNSUPPORTED;
+    if (Hq % Hkv != 0) return GQA_ERR_UNSUPPORTED;  // S may be any length: partial tiles are masked
     if ((size_t)B * Hq * S >= (size_t)1 << 31) return GQA_ERR_UNSUPPORTED;  // TMA row coordinate is 32-bit
     return GQA_OK;
 }

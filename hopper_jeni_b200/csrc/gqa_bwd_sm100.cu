@@ -194,14 +194,17 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     const int qt0 = p.causal ? kt : 0;
     const int n_qt = p.n_tiles - qt0;
     const int n_iter = p.G * n_qt;
-    const int kv_row0 = (b * p.Hkv + hkv) * p.S + kt * kTile;
-    const int q_head0 = b * p.Hq + hkv * p.G;  // first query head of the group
-    auto q_row_of = [&](int it) { return (q_head0 + it / n_qt) * p.S + (qt0 + it % n_qt) * kTile; };  // [B,Hq,S] order
-    // Tensor-map coordinates of the bf16 tiles.  [B,H,S,D] is a [B*H*S, D] matrix: x = 0, y = the flattened row;
-    // [B,S,H,D] is a [B*S, H*D] matrix: x = head * D, y = b * S + s.  The workspace arrays keep [B,Hq,S] order.
-    const int kv_x = p.bshd ? hkv * D : 0, kv_y = p.bshd ? b * p.S + kt * kTile : kv_row0;
-    auto q_x_of = [&](int it) { return p.bshd ? (hkv * p.G + it / n_qt) * D : 0; };
-    auto q_y_of = [&](int it) { return p.bshd ? b * p.S + (qt0 + it % n_qt) * kTile : q_row_of(it); };
+    // Tensor-map coordinates (x = column, y = position in the sequence, z = matrix).  [B,H,S,D] is B*H matrices
+    // [S, D]; [B,S,H,D] is B matrices [S, H*D] with the head at x = head * D.  The workspace arrays are B*Hq
+    // matrices [S, .].  Rows at y >= S read as zeros and are skipped by the reductions, so S may be any length:
+    // keys beyond S give zero rows of K and V (their dK / dV rows are not stored and their dS meets a zero row of
+    // K in dQ), queries beyond S give zero rows of Q, dO and of the -LSE / -Delta columns (P = 1, dS = 0).
+    const int kv_x = p.bshd ? hkv * D : 0, kv_z = p.bshd ? b : b * p.Hkv + hkv;
+    auto head_of = [&](int it) { return hkv * p.G + it / n_qt; };        // query head inside the batch
+    auto q_y_of = [&](int it) { return (qt0 + it % n_qt) * kTile; };     // first query position of the tile
+    auto q_x_of = [&](int it) { return p.bshd ? head_of(it) * D : 0; };
+    auto q_z_of = [&](int it) { return p.bshd ? b : b * p.Hq + head_of(it); };
+    auto ws_z_of = [&](int it) { return b * p.Hq + head_of(it); };
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -253,11 +256,11 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tma_prefetch_desc(&mapDltCol);
             mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
             for (int pn = 0; pn < Cfg::kPanels; ++pn) {
-                tma_load_2d(sK + pn * kPanel, &mapK, kv_full, kv_x + pn * 64, kv_y);
-                tma_load_2d(sV + pn * kPanel, &mapV, kv_full, kv_x + pn * 64, kv_y);
+                tma_load_3d(sK + pn * kPanel, &mapK, kv_full, kv_x + pn * 64, kt * kTile, kv_z);
+                tma_load_3d(sV + pn * kPanel, &mapV, kv_full, kv_x + pn * 64, kt * kTile, kv_z);
             }
             for (int it = 0; it < n_iter; ++it) {
-                const int row = q_row_of(it), qx = q_x_of(it), qy = q_y_of(it);
+                const int qx = q_x_of(it), qy = q_y_of(it), qz = q_z_of(it), wz = ws_z_of(it);
                 {
                     const int st = it % Cfg::kQStages;
                     const uint32_t use = it / Cfg::kQStages;
@@ -265,8 +268,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     // the -LSE/scale columns of the tile ride with Q (both are operands of S^T)
                     mbar_expect_tx(&q_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                        tma_load_2d(sQ + st * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[st], qx + pn * 64, qy);
-                    tma_load_2d(sLseCol + st * Cfg::kColPanel, &mapLseCol, &q_full[st], 0, row);
+                        tma_load_3d(sQ + st * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[st], qx + pn * 64, qy, qz);
+                    tma_load_3d(sLseCol + st * Cfg::kColPanel, &mapLseCol, &q_full[st], 0, qy, wz);
                 }
                 {
                     const int st = it % Cfg::kDOStages;
@@ -275,8 +278,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     // the -Delta columns ride with dO (both are operands of dP^T)
                     mbar_expect_tx(&do_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                        tma_load_2d(sDO + st * Cfg::kTileBytes + pn * kPanel, &mapDO, &do_full[st], qx + pn * 64, qy);
-                    tma_load_2d(sDltCol + st * Cfg::kColPanel, &mapDltCol, &do_full[st], 0, row);
+                        tma_load_3d(sDO + st * Cfg::kTileBytes + pn * kPanel, &mapDO, &do_full[st], qx + pn * 64, qy, qz);
+                    tma_load_3d(sDltCol + st * Cfg::kColPanel, &mapDltCol, &do_full[st], 0, qy, wz);
                 }
             }
         }
@@ -428,8 +431,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             }
         };
         for (int it = 0; it < n_iter; ++it) {
-            const int row = q_row_of(it) + warp * 32;
-            unsigned int* turn = p.dq_turn ? p.dq_turn + (row >> 5) : nullptr;
+            const int row = q_y_of(it) + warp * 32, wz = ws_z_of(it);  // first query position of this warp's slice
+            unsigned int* turn = p.dq_turn ? p.dq_turn + ((size_t)wz * p.n_tiles + row / kTile) * 4 + warp : nullptr;
             bool turn_mine = (turn == nullptr);  // becomes true once this warp may reduce into the slice
             // first look at the counter now: its round trip to L2 hides behind the TMEM loads and the staging
             const unsigned int early = (turn && lane == 0) ? ld_acquire_gpu(turn) : 0xffffffffu;
@@ -449,7 +452,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 };
                 auto reduce_box = [&](int chunk) {  // then wait until the box may be overwritten
                     if (turn_mine && lane == 0) {
-                        tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage, chunk * 32, row);
+                        tma_reduce_add_3d(&mapDQ, sDQ + warp * kWarpStage, chunk * 32, row, wz);
                         bulk_commit_group();
                         bulk_wait_read_all();
                     }
@@ -501,7 +504,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     if (turn_mine && lane == 0) {
     #pragma unroll
                         for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)
-                            tma_reduce_add_2d(&mapDQ, sDQ + warp * kWarpStage + bx * 4096, (rnd * Cfg::kDqBoxes + bx) * 32, row);
+                            tma_reduce_add_3d(&mapDQ, sDQ + warp * kWarpStage + bx * 4096, (rnd * Cfg::kDqBoxes + bx) * 32, row, wz);
                         bulk_commit_group();
                         bulk_wait_read_all();  // staging boxes may be overwritten after this
                     }
@@ -658,9 +661,14 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (ok) ok = mbar_wait(acc_full, 0, ctx, 55);
         if (ok) {
             tc_fence_after_sync();
+            // key rows beyond the end of the sequence are not stored (the TMEM loads below are warp-wide
+            // instructions: every lane runs them, only the stores are guarded)
+            const bool row_ok = kt * kTile + j < p.S;
             constexpr int kQuarter = D / Cfg::kEwGroups;  // columns of dV / dK per warpgroup
             // element offset of this key row in dK / dV
-            const size_t kv_elem = p.bshd ? ((size_t)(kv_y + j) * p.Hkv + hkv) * D : ((size_t)kv_row0 + j) * D;
+            const size_t kv_pos = (size_t)kt * kTile + j;
+            const size_t kv_elem = p.bshd ? (((size_t)b * p.S + kv_pos) * p.Hkv + hkv) * D
+                                          : (((size_t)b * p.Hkv + hkv) * p.S + kv_pos) * D;
 #pragma unroll 1
             for (int which = 0; which < 2; ++which) {
                 const uint32_t tA = tmem + lane_addr + (which == 0 ? Cfg::kColDV : Cfg::kColDK) + w * kQuarter;
@@ -678,7 +686,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                         o.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * mul, __uint_as_float(v[8 * i + 3]) * mul);
                         o.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * mul, __uint_as_float(v[8 * i + 5]) * mul);
                         o.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * mul, __uint_as_float(v[8 * i + 7]) * mul);
-                        *reinterpret_cast<uint4*>(dst + ch * 16 + i * 8) = o;
+                        if (row_ok) *reinterpret_cast<uint4*>(dst + ch * 16 + i * 8) = o;
                     }
                 }
             }
@@ -700,24 +708,25 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
                  unsigned int* status, cudaStream_t stream) {
     using Cfg = BwdCfg<D>;
     CUtensorMap mq, mk, mv, mdo;
-    // rows x columns of the matrix each bf16 tensor is (see the coordinates in the kernel)
-    const uint64_t q_r = s.bshd ? (uint64_t)s.B * s.S : s.q_rows(), q_c = s.bshd ? (uint64_t)s.Hq * D : D;
-    const uint64_t kv_r = s.bshd ? (uint64_t)s.B * s.S : s.kv_rows(), kv_c = s.bshd ? (uint64_t)s.Hkv * D : D;
-    int rc = make_panel_tmap(&mq, Q, q_r, q_c, kTile);
+    // see the coordinates in the kernel
+    const uint64_t S = s.S, qc = s.bshd ? (uint64_t)s.Hq * D : D, kc = s.bshd ? (uint64_t)s.Hkv * D : D;
+    const uint64_t nq = s.bshd ? s.B : (uint64_t)s.B * s.Hq, nkv = s.bshd ? s.B : (uint64_t)s.B * s.Hkv;
+    const uint64_t nws = (uint64_t)s.B * s.Hq;
+    int rc = make_tile3_tmap(&mq, Q, qc, S, nq, S * qc, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mk, K, kv_r, kv_c, kTile);
+    rc = make_tile3_tmap(&mk, K, kc, S, nkv, S * kc, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mv, V, kv_r, kv_c, kTile);
+    rc = make_tile3_tmap(&mv, V, kc, S, nkv, S * kc, kTile);
     if (rc) return rc;
-    rc = make_panel_tmap(&mdo, dO, q_r, q_c, kTile);
+    rc = make_tile3_tmap(&mdo, dO, qc, S, nq, S * qc, kTile);
     if (rc) return rc;
     CUtensorMap mdq;
-    rc = make_f32_box_tmap(&mdq, dq_accum, s.q_rows(), D, 32);
+    rc = make_f32box3_tmap(&mdq, dq_accum, D, S, nws, 32);
     if (rc) return rc;
     CUtensorMap mlse, mdlt;
-    rc = make_col8_tmap(&mlse, lse_cols, s.q_rows(), kTile);
+    rc = make_col8_3_tmap(&mlse, lse_cols, S, nws, kTile);
     if (rc) return rc;
-    rc = make_col8_tmap(&mdlt, delta_cols, s.q_rows(), kTile);
+    rc = make_col8_3_tmap(&mdlt, delta_cols, S, nws, kTile);
     if (rc) return rc;
     GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::kSmemTotal));
@@ -732,7 +741,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.S = s.S;
     p.causal = s.causal;
     p.bshd = s.bshd;
-    p.n_tiles = s.S / kTile;
+    p.n_tiles = (s.S + kTile - 1) / kTile;
     p.G = s.G();
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;

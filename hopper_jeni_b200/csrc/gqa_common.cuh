@@ -38,6 +38,17 @@ int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_
 // one box is a "column panel" (rows of 16 bytes) as make_sdesc_noswizzle expects.
 int make_col8_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_rows);
 
+// 3-D tensor maps over `n_outer` row-major [S, cols] matrices that lie outer_stride elements apart
+// (coordinates: x = column, y = row inside the matrix, z = matrix).  Rows at y >= S are out of bounds: loads
+// read zeros there and stores / reductions skip them, which is what lets S be any length.
+//   tile3: bf16, box = [box_rows, 64 columns], 128-byte swizzle (one box = a panel, as make_panel_tmap).
+//   f32box3: fp32, box = [box_rows, 32 columns], 128-byte swizzle (TMA reduce-add of fp32 tiles).
+//   col8_3: bf16 [S, 8] matrices, box = [box_rows, 8 columns], no swizzle (column panels).
+int make_tile3_tmap(CUtensorMap* out, const void* base, uint64_t cols, uint64_t S, uint64_t n_outer,
+                    uint64_t outer_stride, uint32_t box_rows);
+int make_f32box3_tmap(CUtensorMap* out, const void* base, uint64_t cols, uint64_t S, uint64_t n_outer, uint32_t box_rows);
+int make_col8_3_tmap(CUtensorMap* out, const void* base, uint64_t S, uint64_t n_outer, uint32_t box_rows);
+
 // Device word that forward kernels report bounded-wait failures into (per device).
 int forward_status_word(unsigned int** out);
 

@@ -110,16 +110,16 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     const int hkv = hq / (p.Hq / p.Hkv);
     const int q0 = pair * 2 * kTile;
     const int n_tiles = (q0 + kTile < p.S) ? 2 : 1;
-    const int n_blocks_all = p.S / kTile;
+    const int n_blocks_all = (p.S + kTile - 1) / kTile;  // the last block may be partial: keys at and beyond S are masked
     int n_blk[2];
     n_blk[0] = p.causal ? (q0 / kTile + 1) : n_blocks_all;
     n_blk[1] = (n_tiles == 2) ? (p.causal ? (q0 / kTile + 2) : n_blocks_all) : 0;
     const int n_max = n_blk[1] > n_blk[0] ? n_blk[1] : n_blk[0];
     const int q_row0 = (b * p.Hq + hq) * p.S + q0;   // row in [B,Hq,S] order (LSE)
-    // Tensor-map coordinates of the tiles.  [B,H,S,D] is a [B*H*S, D] matrix: x = 0, y = the flattened row.
-    // [B,S,H,D] is a [B*S, H*D] matrix: x = head * D, y = b * S + s.
-    const int q_x = p.bshd ? hq * D : 0, q_y = p.bshd ? b * p.S + q0 : q_row0;
-    const int kv_x = p.bshd ? hkv * D : 0, kv_y = p.bshd ? b * p.S : (b * p.Hkv + hkv) * p.S;
+    // Tensor-map coordinates (x = column, y = position in the sequence, z = matrix).  [B,H,S,D] is B*H matrices
+    // [S, D]; [B,S,H,D] is B matrices [S, H*D] with the head at x = head * D.  Rows at y >= S read as zeros.
+    const int q_x = p.bshd ? hq * D : 0, q_z = p.bshd ? b : b * p.Hq + hq;
+    const int kv_x = p.bshd ? hkv * D : 0, kv_z = p.bshd ? b : b * p.Hkv + hkv;
 
     // ---- setup ------------------------------------------------------------------
     if (tid == 0) {
@@ -159,7 +159,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             for (int t = 0; t < n_tiles; ++t) {
                 mbar_expect_tx(&q_full[t], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_2d(sQ + t * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[t], q_x + pn * 64, q_y + t * kTile);
+                    tma_load_3d(sQ + t * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[t], q_x + pn * 64, q0 + t * kTile, q_z);
             }
             for (int n = 0; n < n_max; ++n) {
                 const int st = n % Cfg::kStages;
@@ -167,11 +167,11 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 if (use > 0 && !mbar_wait(&k_empty[st], (use - 1) & 1, ctx, 10)) break;
                 mbar_expect_tx(&k_full[st], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_2d(sK + st * Cfg::kTileBytes + pn * kPanel, &mapK, &k_full[st], kv_x + pn * 64, kv_y + n * kTile);
+                    tma_load_3d(sK + st * Cfg::kTileBytes + pn * kPanel, &mapK, &k_full[st], kv_x + pn * 64, n * kTile, kv_z);
                 if (use > 0 && !mbar_wait(&v_empty[st], (use - 1) & 1, ctx, 11)) break;
                 mbar_expect_tx(&v_full[st], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_2d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], kv_x + pn * 64, kv_y + n * kTile);
+                    tma_load_3d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], kv_x + pn * 64, n * kTile, kv_z);
             }
         }
     } else if (warp >= kWarpMma0) {
@@ -251,7 +251,11 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 if (warp == 0) GQA_FTRACE(0, j, 0);
                 if (warp == 4) GQA_FTRACE(2, j, 0);
                 if (t == 0) GQA_FTRACE(4, j, warp & 3);
-                const bool masked = p.causal && (n == diag_block);
+                // last valid column of this row inside the 128-key block: the causal diagonal and / or the end of S
+                const bool diag = p.causal && (n == diag_block);
+                const int s_left = p.S - n * kTile;  // keys of this block that exist
+                const bool masked = diag || s_left < kTile;
+                const int lim = min(diag ? r : kTile - 1, s_left - 1);
                 const int col0 = h * kHalf;  // column of v[0] inside the 128-key block
                 // the 64-column half row of S into registers (one TMEM round trip), then the row maximum with
                 // four independent chains of three-input maxima
@@ -265,7 +269,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     if (masked) {
 #pragma unroll
                         for (int i = 0; i < kHalf; ++i)
-                            m4[i & 3] = (col0 + i > r) ? m4[i & 3] : fmaxf(m4[i & 3], __uint_as_float(v[i]));
+                            m4[i & 3] = (col0 + i > lim) ? m4[i & 3] : fmaxf(m4[i & 3], __uint_as_float(v[i]));
                     } else {
 #pragma unroll
                         for (int i = 0; i < kHalf; i += 2)
@@ -333,8 +337,8 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                             const int cc = col0 + ch * 32 + 2 * i;
                             float e0 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i]), c, -mc));
                             float e1 = ex2_approx(fmaf(__uint_as_float(v[ch * 32 + 2 * i + 1]), c, -mc));
-                            if (cc > r) e0 = 0.f;
-                            if (cc + 1 > r) e1 = 0.f;
+                            if (cc > lim) e0 = 0.f;
+                            if (cc + 1 > lim) e1 = 0.f;
                             l4[i & 3] += e0 + e1;
                             pk[i] = pack_bf16x2(e0, e1);
                         }
@@ -354,9 +358,12 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             if (ok) ok = mbar_wait(&o_full[t], 0, ctx, 31);
             if (ok) {
                 tc_fence_after_sync();
+                // rows beyond the end of the sequence are not stored (the TMEM loads below are warp-wide
+                // instructions: every lane runs them, only the stores are guarded)
+                const bool row_ok = q0 + t * kTile + r < p.S;
                 const float inv_l = 1.0f / l_run;
                 const size_t grow_ = (size_t)q_row0 + t * kTile + r;
-                __nv_bfloat16* orow = p.bshd ? p.O + ((size_t)(q_y + t * kTile + r) * p.Hq + hq) * D : p.O + grow_ * D;
+                __nv_bfloat16* orow = p.bshd ? p.O + ((size_t)(b * p.S + q0 + t * kTile + r) * p.Hq + hq) * D : p.O + grow_ * D;
 #pragma unroll 1
                 for (int ch = 0; ch < D / 32; ++ch) {
                     uint32_t v[32];
@@ -369,10 +376,10 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                         o.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * inv_l, __uint_as_float(v[8 * i + 3]) * inv_l);
                         o.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * inv_l, __uint_as_float(v[8 * i + 5]) * inv_l);
                         o.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * inv_l, __uint_as_float(v[8 * i + 7]) * inv_l);
-                        *reinterpret_cast<uint4*>(orow + ch * 32 + i * 8) = o;
+                        if (row_ok) *reinterpret_cast<uint4*>(orow + ch * 32 + i * 8) = o;
                     }
                 }
-                if (p.LSE) p.LSE[grow_] = (m_run * c + log2f(l_run)) * kLn2;
+                if (p.LSE && row_ok) p.LSE[grow_] = (m_run * c + log2f(l_run)) * kLn2;
             }
         }
     }
@@ -391,13 +398,14 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
                  cudaStream_t stream) {
     using Cfg = FwdCfg<D>;
     CUtensorMap mq, mk, mv;
-    // rows x columns of the matrix each tensor is (see the coordinates in the kernel)
-    const uint64_t bs = (uint64_t)s.B * s.S;
-    int rc = s.bshd ? make_panel_tmap(&mq, Q, bs, (uint64_t)s.Hq * D, kTile) : make_panel_tmap(&mq, Q, s.q_rows(), D, kTile);
+    // see the coordinates in the kernel
+    const uint64_t S = s.S, qc = s.bshd ? (uint64_t)s.Hq * D : D, kc = s.bshd ? (uint64_t)s.Hkv * D : D;
+    const uint64_t nq = s.bshd ? s.B : (uint64_t)s.B * s.Hq, nkv = s.bshd ? s.B : (uint64_t)s.B * s.Hkv;
+    int rc = make_tile3_tmap(&mq, Q, qc, S, nq, S * qc, kTile);
     if (rc) return rc;
-    rc = s.bshd ? make_panel_tmap(&mk, K, bs, (uint64_t)s.Hkv * D, kTile) : make_panel_tmap(&mk, K, s.kv_rows(), D, kTile);
+    rc = make_tile3_tmap(&mk, K, kc, S, nkv, S * kc, kTile);
     if (rc) return rc;
-    rc = s.bshd ? make_panel_tmap(&mv, V, bs, (uint64_t)s.Hkv * D, kTile) : make_panel_tmap(&mv, V, s.kv_rows(), D, kTile);
+    rc = make_tile3_tmap(&mv, V, kc, S, nkv, S * kc, kTile);
     if (rc) return rc;
     GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_fwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::kSmemTotal));

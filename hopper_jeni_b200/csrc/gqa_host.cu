@@ -58,8 +58,10 @@ struct TmapKey {
     const void* base;
     uint64_t rows, cols;
     uint32_t box_rows, kind;
+    uint64_t n_outer = 0, outer_stride = 0;  // 3-D maps only
     bool operator==(const TmapKey& o) const {
-        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && kind == o.kind;
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && kind == o.kind &&
+               n_outer == o.n_outer && outer_stride == o.outer_stride;
     }
 };
 struct TmapCache {
@@ -145,6 +147,45 @@ int make_col8_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint32_t b
     return GQA_OK;
 }
 
+namespace {
+// kind: 3 = bf16 tile, 4 = fp32 box, 5 = bf16 column panel
+int make_tmap3(CUtensorMap* out, const void* base, uint64_t cols, uint64_t S, uint64_t n_outer, uint64_t outer_stride,
+               uint32_t box_cols, uint32_t box_rows, uint32_t kind) {
+    const TmapKey key{base, S, cols, box_rows, kind, n_outer, outer_stride};
+    if (g_tmaps.find(key, out)) return GQA_OK;
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
+        return GQA_ERR_CUDA;
+    }
+    const bool f32 = (kind == 4);
+    const uint64_t esz = f32 ? sizeof(float) : sizeof(__nv_bfloat16);
+    cuuint64_t dims[3] = {cols, S, n_outer};
+    cuuint64_t strides[2] = {cols * esz, outer_stride * esz};
+    cuuint32_t box[3] = {box_cols, box_rows, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    kind == 5 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                    kind == 5 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled(3-D)");
+    g_tmaps.put(key, *out);
+    return GQA_OK;
+}
+}  // namespace
+
+int make_tile3_tmap(CUtensorMap* out, const void* base, uint64_t cols, uint64_t S, uint64_t n_outer,
+                    uint64_t outer_stride, uint32_t box_rows) {
+    return make_tmap3(out, base, cols, S, n_outer, outer_stride, 64u, box_rows, 3u);
+}
+int make_f32box3_tmap(CUtensorMap* out, const void* base, uint64_t cols, uint64_t S, uint64_t n_outer, uint32_t box_rows) {
+    return make_tmap3(out, base, cols, S, n_outer, S * cols, 32u, box_rows, 4u);
+}
+int make_col8_3_tmap(CUtensorMap* out, const void* base, uint64_t S, uint64_t n_outer, uint32_t box_rows) {
+    return make_tmap3(out, base, 8, S, n_outer, S * 8, 8u, box_rows, 5u);
+}
+
 int forward_status_word(unsigned int** out) {
     constexpr int kMaxDev = 64;
     static unsigned int* words[kMaxDev] = {};
@@ -169,7 +210,7 @@ extern "C" const char* gqa_status_string(int status) {
     switch (status) {
         case GQA_OK: return "ok";
         case GQA_ERR_BAD_ARGUMENT: return "bad argument (null, non-positive or misaligned)";
-        case GQA_ERR_UNSUPPORTED: return "unsupported shape (need D in {64,128}, S % 128 == 0, Hq % Hkv == 0)";
+        case GQA_ERR_UNSUPPORTED: return "unsupported shape (need D in {64,128}, Hq % Hkv == 0, B*Hq*S < 2^31)";
         case GQA_ERR_WORKSPACE: return "workspace missing or too small";
         case GQA_ERR_CUDA: return "CUDA call failed";
         case GQA_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";

@@ -21,7 +21,8 @@ struct Shape {
 struct BwdWorkspace {
     // lse_cols / delta_cols: per query row eight bf16 (16 bytes): a three-way bf16 split of -LSE/scale and of
     // -Delta in the first three, zeros after; they enter the S^T and dP^T products as one extra K step.
-    // dq_turn: one counter per 32 query rows, used only by the deterministic mode (order of the dQ reductions).
+    // dq_turn: one counter per 32-row slice of a query tile, used only by the deterministic mode (order of the dQ
+    // reductions).
     size_t status_off, lse_cols_off, delta_cols_off, dq_turn_off, dq_turn_bytes, dq_accum_off, total;
     explicit BwdWorkspace(const Shape& s) {
         auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
@@ -29,7 +30,7 @@ struct BwdWorkspace {
         lse_cols_off = 256;
         delta_cols_off = lse_cols_off + up(s.q_rows() * 16);
         dq_turn_off = delta_cols_off + up(s.q_rows() * 16);
-        dq_turn_bytes = s.q_rows() / 32 * sizeof(unsigned int);
+        dq_turn_bytes = (size_t)s.B * s.Hq * ((s.S + 127) / 128) * 4 * sizeof(unsigned int);  // per tile and drain warp
         dq_accum_off = dq_turn_off + up(dq_turn_bytes);
         total = dq_accum_off + up(s.q_rows() * (size_t)s.D * sizeof(float));
     }

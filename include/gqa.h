@@ -7,8 +7,10 @@
  *   K, V, dK, dV : [B, Hkv, S, D]  bf16, contiguous, row-major
  *   LSE          : [B, Hq, S]      fp32, natural log of sum_j exp(scale * q_i . k_j)
  *   query head hq reads KV head hq / (Hq / Hkv)
- * Supported: D in {64, 128}, S a multiple of 128, Hq a multiple of Hkv, all
- * pointers 16-byte aligned.  Anything else returns an error code; the library
+ * Supported: D in {64, 128}, any S >= 1 (the reference needs S % 64 == 0 in the backward,
+ * src/attention/GQA_bwd_baseline.cu:549-602, and S % 256 == 0 in the forward,
+ * src/attention/GQA_fwd_ref.cu:352; here a partial last tile is masked), Hq a multiple of Hkv,
+ * all pointers 16-byte aligned.  Anything else returns an error code; the library
  * never exits the process and never traps the device.
  *
  * All functions return GQA_OK (0) or a negative gqa_status.  Work is enqueued
@@ -29,7 +31,7 @@ typedef struct CUstream_st* gqa_stream_t; /* same handle as cudaStream_t */
 typedef enum gqa_status {
     GQA_OK = 0,
     GQA_ERR_BAD_ARGUMENT = -1,   /* null pointer, non-positive size, misaligned pointer */
-    GQA_ERR_UNSUPPORTED = -2,    /* shape outside the supported set (D, S % 128, Hq % Hkv) */
+    GQA_ERR_UNSUPPORTED = -2,    /* shape outside the supported set (D in {64,128}, Hq % Hkv == 0) */
     GQA_ERR_WORKSPACE = -3,      /* workspace missing or smaller than gqa_bwd_workspace_bytes() */
     GQA_ERR_CUDA = -4,           /* a CUDA runtime/driver call failed (see gqa_last_cuda_error) */
     GQA_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up; outputs are invalid */

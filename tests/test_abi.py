@@ -41,14 +41,14 @@ def test_workspace_bytes_formula(gqa_lib):
     assert need % 256 == 0
     # unsupported shapes report zero
     assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 96, 0) == 0
-    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S + 64, D, 0) == 0
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S + 60, D, 0) > need   # any S: partial tiles are masked
     assert gqa_lib.gqa_bwd_workspace_bytes(B, 10, 4, S, D, 0) == 0
 
 
 def test_argument_validation_needs_no_device(gqa_lib):
     p = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
     assert gqa_lib.gqa_fwd(None, p, p, p, None, 1, 4, 2, 128, 64, 0, 0.125, None) == -1
-    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 100, 64, 0, 0.125, None) == -2      # S % 128
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 0, 64, 0, 0.125, None) == -1        # S <= 0
     assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 128, 80, 0, 0.125, None) == -2      # D
     assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 5, 2, 128, 64, 0, 0.125, None) == -2      # Hq % Hkv
     assert gqa_lib.gqa_fwd(p, p, p, p, None, 0, 4, 2, 128, 64, 0, 0.125, None) == -1      # B <= 0

@@ -46,4 +46,5 @@ def test_plugins_pass_the_harness_gate(gqa_lib, shape):
     assert _gate(fwd.make(q, k, v, shape)(), ref)
     dq, dk, dv = bwd.make_bwd(q, k, v, do, shape)()
     assert _gate(dq, q32.grad) and _gate(dk, k32.grad) and _gate(dv, v32.grad)
-    assert fwd.available(Shape(1, 4, 2, 100, 64)) [0] is False
+    assert fwd.available(Shape(1, 4, 2, 100, 64))[0] is True      # any sequence length
+    assert fwd.available(Shape(1, 4, 2, 128, 96))[0] is False     # head dims other than 64 and 128

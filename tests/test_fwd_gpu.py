@@ -90,7 +90,12 @@ def test_forward_headline_shape_properties(gqa_lib):
 
 
 def test_forward_rejects_unsupported_shapes(gqa_lib):
-    q = torch.zeros(1, 2, 192, 64, dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros(1, 2, 192, 96, dtype=torch.bfloat16, device="cuda")   # head dim other than 64 / 128
     with pytest.raises(capi.GqaError) as e:
         ops.gqa_forward(q, q, q)
+    assert e.value.status == -2
+    q = torch.zeros(1, 3, 128, 64, dtype=torch.bfloat16, device="cuda")   # Hq not a multiple of Hkv
+    k = torch.zeros(1, 2, 128, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(capi.GqaError) as e:
+        ops.gqa_forward(q, k, k)
     assert e.value.status == -2
