@@ -60,7 +60,7 @@ int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE,
  * gqa_fwd with option flags.  flags = 0 is gqa_fwd.
  * GQA_LAYOUT_BSHD: Q and O are [B,S,Hq,D] and K and V [B,S,Hkv,D] (sequence-major, the layout the reference's
  * harness hands to the FlashAttention and FlashInfer adapters, harness/competitors.py:116-122) instead of the
- * canonical [B,H,S,D]; the tiles are fetched through tensor maps over the [B*S, H*D] matrix, so no transposed
+ * canonical [B,H,S,D]; the tiles are fetched through tensor maps over the B matrices [S, H*D], so no transposed
  * copy is made.  LSE stays [B,Hq,S].  Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
  */
 #define GQA_LAYOUT_BSHD 2u
