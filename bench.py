@@ -38,9 +38,9 @@ HEADLINE = dict(B=8, Hq=12, Hkv=4, S=4096, D=64, causal=False)
 METRIC = "GQA bwd TFLOP/s (B8 Hq12 Hkv4 S4096 D64 bf16)"
 NOMINAL_BF16_TFLOPS = 2250.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the backward main kernel from one ncu capture at B=4
-# (B4 Hq12 Hkv4 S4096 D64: 596 MB), scaled by 2 to the headline batch: the (batch, KV-head)
-# groups are independent, so traffic grows in proportion to B.
-MAIN_KERNEL_DRAM_BYTES_PER_LAUNCH = 2 * 596.0e6
+# (B4 Hq12 Hkv4 S4096 D64: 123.8 MB read + 30.3 MB written = 154 MB), scaled by 2 to the headline batch: the
+# (batch, KV-head) groups are independent, so traffic grows in proportion to B.
+MAIN_KERNEL_DRAM_BYTES_PER_LAUNCH = 2 * 154.2e6
 
 
 def bwd_flops(B, Hq, S, D, causal):
