@@ -11,22 +11,26 @@ from . import ops
 
 class _GqaAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
+    def forward(ctx, q, k, v, causal, scale, layout, deterministic):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse = ops.gqa_forward(q, k, v, causal=causal, scale=scale)
+        o, lse = ops.gqa_forward(q, k, v, causal=causal, scale=scale, layout=layout)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.causal, ctx.scale = causal, scale
+        ctx.causal, ctx.scale, ctx.layout, ctx.deterministic = causal, scale, layout, deterministic
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = ops.gqa_backward(q, k, v, o, do.contiguous(), lse, causal=ctx.causal, scale=ctx.scale)
-        return dq, dk, dv, None, None
+        dq, dk, dv = ops.gqa_backward(q, k, v, o, do.contiguous(), lse, causal=ctx.causal, scale=ctx.scale,
+                                      layout=ctx.layout, deterministic=ctx.deterministic)
+        return dq, dk, dv, None, None, None, None
 
 
-def gqa_attention(q, k, v, causal: bool = False, scale: float | None = None):
+def gqa_attention(q, k, v, causal: bool = False, scale: float | None = None, layout: str = "bhsd",
+                  deterministic: bool = False):
     """Differentiable GQA attention on bf16 CUDA tensors ``[B,Hq,S,D]`` / ``[B,Hkv,S,D]``; same semantics as
-    ``F.scaled_dot_product_attention(q, k, v, scale=scale, is_causal=causal, enable_gqa=True)``."""
+    ``F.scaled_dot_product_attention(q, k, v, scale=scale, is_causal=causal, enable_gqa=True)``.
+    ``layout="bshd"`` takes and returns ``[B,S,H,D]`` tensors; ``deterministic`` makes the gradient of q
+    bit-reproducible (the other two always are)."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else float(scale)
-    return _GqaAttention.apply(q, k, v, bool(causal), scale)
+    return _GqaAttention.apply(q, k, v, bool(causal), scale, layout, bool(deterministic))

@@ -21,3 +21,25 @@ def test_autograd_wrapper_matches_fp32_sdpa(gqa_lib, causal):
     F.scaled_dot_product_attention(q32, k32, v32, is_causal=causal, enable_gqa=True).backward(do.float())
     for got, ref, name in ((q.grad, q32.grad, "dQ"), (k.grad, k32.grad, "dK"), (v.grad, v32.grad, "dV")):
         util.assert_close_bf16(util.to_np(got), util.to_np(ref), name, util.REL_RMS_BWD)
+
+
+def test_autograd_wrapper_sequence_major_ragged_deterministic(gqa_lib):
+    """[B,S,H,D] tensors, a sequence length that is not a multiple of the tile, ordered dQ reductions: the
+    gradients match fp32 SDPA autograd and two runs give the same bits."""
+    B, Hq, Hkv, S, D = 1, 4, 2, 300, 128
+    g = torch.Generator(device="cuda").manual_seed(6)
+    q, k, v = (torch.randn(B, S, h, D, generator=g, device="cuda").bfloat16().requires_grad_(True) for h in (Hq, Hkv, Hkv))
+    do = torch.randn(B, S, Hq, D, generator=g, device="cuda").bfloat16()
+    grads = []
+    for _ in range(2):
+        for t in (q, k, v):
+            t.grad = None
+        gqa_attention(q, k, v, causal=True, layout="bshd", deterministic=True).backward(do)
+        grads.append([t.grad.clone() for t in (q, k, v)])
+    for a, b2 in zip(*grads):
+        assert torch.equal(a, b2)
+    q32, k32, v32 = (t.detach().float().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+    F.scaled_dot_product_attention(q32, k32, v32, is_causal=True, enable_gqa=True).backward(do.float().transpose(1, 2))
+    for got, ref, name in zip(grads[0], (q32.grad, k32.grad, v32.grad), ("dQ", "dK", "dV")):
+        util.assert_close_bf16(util.to_np(got.transpose(1, 2).contiguous()), util.to_np(ref.contiguous()), name,
+                               util.REL_RMS_BWD)
