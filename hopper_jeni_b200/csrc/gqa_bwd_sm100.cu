@@ -69,7 +69,7 @@ struct BwdCfg {
     static constexpr int kTileBytes = kPanels * kPanel;
     // Elementwise warpgroups: four at D = 64 (32 query columns per thread).  At D = 128 two (64 columns per
     // thread): the tensor work per tile pair doubles while the elementwise work does not, and the smaller CTA
-    // (16 instead of 25 warps) leaves 128 registers per thread, which the dQ drain needs (see kDrainEarlyRelease).
+    // (16 instead of 24 warps) leaves 128 registers per thread, which the dQ drain needs (see kDrainEarlyRelease).
     static constexpr int kEwGroups = (D == 64) ? 4 : 2;
     static constexpr int kCols = kTile / kEwGroups;       // query columns per elementwise thread
     static constexpr int kHalves = kCols / 16;            // 16-column steps per thread and stage

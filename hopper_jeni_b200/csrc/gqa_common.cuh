@@ -27,16 +27,8 @@ int note_device_timeout(unsigned int word);
     } while (0)
 
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix, box = [box_rows, 64 columns],
-// 128-byte swizzle: one box is a panel of box_rows rows x 128 bytes.
+// 128-byte swizzle: one box is a panel of box_rows rows x 128 bytes (used by the UMMA self test).
 int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
-
-// 2-D fp32 tensor map over a row-major [rows, cols] matrix, box = [box_rows, 32 columns] (128 bytes wide),
-// 128-byte swizzle; used for TMA reduce-add of fp32 tiles.
-int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
-
-// 2-D bf16 tensor map over a row-major [rows, 8] matrix (16 bytes per row), box = [box_rows, 8 columns], no swizzle:
-// one box is a "column panel" (rows of 16 bytes) as make_sdesc_noswizzle expects.
-int make_col8_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_rows);
 
 // 3-D tensor maps over `n_outer` row-major [S, cols] matrices that lie outer_stride elements apart
 // (coordinates: x = column, y = row inside the matrix, z = matrix).  Rows at y >= S are out of bounds: loads

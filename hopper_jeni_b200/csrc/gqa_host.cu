@@ -107,46 +107,6 @@ int make_panel_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
     return GQA_OK;
 }
 
-int make_f32_box_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    const TmapKey key{base, rows, cols, box_rows, 1u};
-    if (g_tmaps.find(key, out)) return GQA_OK;
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) {
-        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
-        return GQA_ERR_CUDA;
-    }
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * sizeof(float)};
-    cuuint32_t box[2] = {32u, box_rows};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled(f32)");
-    g_tmaps.put(key, *out);
-    return GQA_OK;
-}
-
-int make_col8_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_rows) {
-    const TmapKey key{base, rows, 8, box_rows, 2u};
-    if (g_tmaps.find(key, out)) return GQA_OK;
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) {
-        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
-        return GQA_ERR_CUDA;
-    }
-    cuuint64_t dims[2] = {8, rows};
-    cuuint64_t strides[1] = {8 * sizeof(__nv_bfloat16)};
-    cuuint32_t box[2] = {8u, box_rows};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return note_driver_error(r, "cuTensorMapEncodeTiled(col8)");
-    g_tmaps.put(key, *out);
-    return GQA_OK;
-}
-
 namespace {
 // kind: 3 = bf16 tile, 4 = fp32 box, 5 = bf16 column panel
 int make_tmap3(CUtensorMap* out, const void* base, uint64_t cols, uint64_t S, uint64_t n_outer, uint64_t outer_stride,
