@@ -1,7 +1,8 @@
-"""ctypes binding of the C ABI declared in ``include/gqa.h``.
+"""ctypes binding of the C ABI declared in ``include/gqa.h`` (``libgqa_b200.so``, the product) and in
+``include/gqa_selftest.h`` (``libgqa_b200_selftest.so``, diagnostics used by the test-suite only).
 
-Signatures here must stay in lock-step with that header; ``EXPORTS`` lists every symbol the header
-declares and the test-suite checks that the built library exports each of them.
+Signatures here must stay in lock-step with those headers; ``EXPORTS`` / ``SELFTEST_EXPORTS`` list every
+symbol each header declares and the test-suite checks that the built libraries export each of them.
 """
 from __future__ import annotations
 
@@ -10,6 +11,7 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
+_SELFTEST_LIB = None
 
 GQA_OK = 0
 GQA_BWD_DETERMINISTIC = 1
@@ -40,11 +42,16 @@ EXPORTS = {
     "gqa_last_cuda_error": (ctypes.c_char_p, []),
     "gqa_launch_count": (ctypes.c_ulonglong, []),
     "gqa_version": (ctypes.c_char_p, []),
+}
+
+#: symbol -> (restype, argtypes); one entry per declaration in include/gqa_selftest.h
+SELFTEST_EXPORTS = {
     "gqa_selftest_umma": (_i, [_vp, _vp, _fp, _i, _i, _i, _vp]),
     "gqa_selftest_umma_cycles": (_i, [_vp, _vp, _fp, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_float), _vp]),
     "gqa_checker_fwd_simt": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_checker_bwd_simt": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _fp,
                                   _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "gqa_selftest_timeout": (_i, [_vp, ctypes.c_longlong, _i, _vp]),
 }
 
 
@@ -70,13 +77,34 @@ def load_library():
             raise FileNotFoundError(
                 f"{path} not found: build it with `python -m hopper_jeni_b200.build` (needs nvcc); "
                 "this package has no CPU or framework fallback")
-        lib = ctypes.CDLL(path)
+        lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
         for name, (res, args) in EXPORTS.items():
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
         _LIB = lib
     return _LIB
+
+
+def selftest_lib_path() -> str:
+    return os.path.join(os.path.dirname(lib_path()), "libgqa_b200_selftest.so")
+
+
+def load_selftest_library():
+    """Load the diagnostics library (checker kernels, self tests); it links against the product library."""
+    global _SELFTEST_LIB
+    if _SELFTEST_LIB is None:
+        load_library()  # resolves its dependency and fails first if the product is missing
+        path = selftest_lib_path()
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} not found: build it with `python -m hopper_jeni_b200.build`")
+        lib = ctypes.CDLL(path)
+        for name, (res, args) in SELFTEST_EXPORTS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _SELFTEST_LIB = lib
+    return _SELFTEST_LIB
 
 
 def check(fn: str, status: int) -> None:

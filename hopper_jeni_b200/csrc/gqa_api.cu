@@ -1,6 +1,5 @@
 // C-ABI entry points: argument validation, workspace carve-up and the launch
-// sequence of each operator.  No allocation happens on the hot path (the forward
-// status word is created once per device on first use).
+// sequence of each operator.  Nothing here allocates device memory.
 #include <mutex>
 
 #include "gqa_common.cuh"
@@ -23,6 +22,10 @@ int check_device() {
     return cached_rc;
 }
 
+// scale enters as 1/scale (the folded LSE term of the backward) and as the sign convention of the forward's
+// running maximum: it must be finite and positive.
+bool scale_ok(float scale) { return scale > 0.f && scale < INFINITY; }
+
 int check_shape(int B, int Hq, int Hkv, int S, int D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0) return GQA_ERR_BAD_ARGUMENT;
     if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
@@ -38,7 +41,7 @@ namespace {
 int run_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv, int S, int D,
             int causal, float scale, cudaStream_t stream, unsigned int flags) {
     if (flags & ~(unsigned)GQA_LAYOUT_BSHD) return GQA_ERR_BAD_ARGUMENT;
-    if (!Q || !K || !V || !O) return GQA_ERR_BAD_ARGUMENT;
+    if (!Q || !K || !V || !O || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
     if (!gqa::aligned16(Q) || !gqa::aligned16(K) || !gqa::aligned16(V) || !gqa::aligned16(O) ||
@@ -85,7 +88,7 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
             void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale, void* workspace,
             size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev, unsigned int flags = 0) {
     if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD)) return GQA_ERR_BAD_ARGUMENT;
-    if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV) return GQA_ERR_BAD_ARGUMENT;
+    if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
     const void* ptrs[] = {Q, K, V, O, dO, LSE, dQ, dK, dV};
@@ -206,6 +209,11 @@ extern "C" int gqa_bwd_static_scratch(const void* Q, const void* K, const void* 
                        need, (size_t)GQA_STATIC_SCRATCH_BYTES);
         return GQA_ERR_WORKSPACE;
     }
+    // the argument and device checks of run_bwd come first, so that a wrong device reports GQA_ERR_ARCH and
+    // not the failed symbol look-up
+    if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
+    rc = check_device();
+    if (rc) return rc;
     void* scratch = nullptr;
     rc = static_scratch_address(&scratch);
     if (rc) return rc;
@@ -218,36 +226,17 @@ extern "C" int gqa_bwd_static_scratch(const void* Q, const void* K, const void* 
 extern "C" int gqa_check_status(const void* workspace, gqa_stream_t stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     const unsigned int* word = static_cast<const unsigned int*>(workspace);
+    unsigned int* forward_word = nullptr;
     if (!word) {
-        unsigned int* w = nullptr;
-        int rc = gqa::forward_status_word(&w);
+        int rc = gqa::forward_status_word(&forward_word);
         if (rc) return rc;
-        word = w;
+        word = forward_word;
     }
     unsigned int host = 0;
     GQA_CUDA_TRY(cudaMemcpyAsync(&host, word, sizeof host, cudaMemcpyDeviceToHost, stream));
     GQA_CUDA_TRY(cudaStreamSynchronize(stream));
-    return host == 0 ? GQA_OK : gqa::note_device_timeout(host);
-}
-
-// ---- CUDA-core checker entry points (diagnostics; see gqa_simt.cu) ----------
-extern "C" int gqa_checker_fwd_simt(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq,
-                                    int Hkv, int S, int D, int causal, float scale, gqa_stream_t stream) {
-    if (!Q || !K || !V || !O) return GQA_ERR_BAD_ARGUMENT;
-    if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0 || D > 128 || Hq % Hkv) return GQA_ERR_UNSUPPORTED;
-    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
-    return gqa::launch_fwd_simt(Q, K, V, O, LSE, s, reinterpret_cast<cudaStream_t>(stream));
-}
-
-extern "C" int gqa_checker_bwd_simt(const void* Q, const void* K, const void* V, const void* O, const void* dO,
-                                    const float* LSE, void* dQ, void* dK, void* dV, float* delta_scratch, int B,
-                                    int Hq, int Hkv, int S, int D, int causal, float scale, gqa_stream_t stream_) {
-    if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !delta_scratch) return GQA_ERR_BAD_ARGUMENT;
-    if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || (D != 64 && D != 128) || Hq % Hkv) return GQA_ERR_UNSUPPORTED;
-    const Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    int rc = gqa::launch_bwd_preprocess(O, dO, nullptr, 0.f, delta_scratch, nullptr, nullptr, nullptr, s.q_rows(), D,
-                                        stream);
-    if (rc) return rc;
-    return gqa::launch_bwd_simt(Q, K, V, dO, LSE, delta_scratch, dQ, dK, dV, s, stream);
+    if (host == 0) return GQA_OK;
+    // the forward's report is sticky: reading it re-arms the device
+    if (forward_word) GQA_CUDA_TRY(cudaMemsetAsync(forward_word, 0, sizeof(unsigned int), stream));
+    return gqa::note_device_timeout(host);
 }

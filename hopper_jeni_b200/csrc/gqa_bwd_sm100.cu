@@ -32,8 +32,9 @@
 //
 // Replaces gqa_bwd_vj1d (src/attention/GQA_bwd_baseline.cu:405-547) in the
 // G-loop-inside-the-CTA form of gqa_bwd_vz2_wgmma (src/attention/GQA_bwd.cu:15207-15342);
-// roundings follow the reference: P and dS are rounded to bf16 before the GEMMs that
-// consume them, dK and dQ are scaled in fp32 (GQA_bwd_baseline.cu:243-255, :320-326, :530-534).
+// roundings follow the reference: P is rounded to bf16 before dV and before the dS product,
+// dS = bf16(P_bf16 * (dP - Delta)) with the product in fp32, dK and dQ are scaled in fp32
+// (GQA_bwd_baseline.cu:243-255, :320-326, :530-534).
 #include "gqa_common.cuh"
 #include "gqa_kernels.cuh"
 #include "sm100_ptx.cuh"
@@ -207,7 +208,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     auto ws_z_of = [&](int it) { return b * p.Hq + head_of(it); };
 
     if (tid == 0) {
-        *abort_flag = 0;
+        // a thread block of this launch that has already given up leaves a non-zero status word: the blocks that
+        // start after it skip their work (see below), so a wedged launch drains in one wave
+        *abort_flag = (*reinterpret_cast<volatile unsigned int*>(p.status) != 0u) ? 98u : 0u;
         mbar_init(kv_full, 1);
         mbar_init(s_full, 1);
         mbar_init(dp_full, 1);
@@ -241,6 +244,10 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (*abort_flag != 0) {  // uniform: every thread reads the flag after the barrier
+        if (warp == Cfg::kWarpMmaS) tmem_dealloc(tmem, Cfg::kTmemCols);
+        return;
+    }
     const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ);
     const uint32_t do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
 
@@ -563,13 +570,20 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 #pragma unroll
             for (int q2 = 0; q2 < 2; ++q2) {
                 const uint32_t* pp = pk + q2 * 4;
-                uint4 o;
-                // (dP - Delta) is rounded to bf16 and multiplied with the bf16 P in one packed instruction: three
-                // instructions per pair instead of five; measured +3 % speed, relative RMS error of dQ/dK 2.9e-3 -> 3.4e-3
-                o.x = mul_bf16x2(pp[0], pack_bf16x2(__uint_as_float(v[q2 * 8 + 0]), __uint_as_float(v[q2 * 8 + 1])));
-                o.y = mul_bf16x2(pp[1], pack_bf16x2(__uint_as_float(v[q2 * 8 + 2]), __uint_as_float(v[q2 * 8 + 3])));
-                o.z = mul_bf16x2(pp[2], pack_bf16x2(__uint_as_float(v[q2 * 8 + 4]), __uint_as_float(v[q2 * 8 + 5])));
-                o.w = mul_bf16x2(pp[3], pack_bf16x2(__uint_as_float(v[q2 * 8 + 6]), __uint_as_float(v[q2 * 8 + 7])));
+                uint32_t o4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#ifdef GQA_BWD_PACKED_DS
+                    // shortcut (not the default): (dP - Delta) rounded to bf16 first, one packed bf16 product;
+                    // two roundings instead of one, about 3 % faster
+                    o4[i] = mul_bf16x2(pp[i], pack_bf16x2(__uint_as_float(v[q2 * 8 + 2 * i]), __uint_as_float(v[q2 * 8 + 2 * i + 1])));
+#else
+                    // dS = bf16(P_bf16 * (dP - Delta)): the product in fp32, one rounding, as the reference does
+                    const float p_lo = __uint_as_float(pp[i] << 16), p_hi = __uint_as_float(pp[i] & 0xffff0000u);
+                    o4[i] = pack_bf16x2(p_lo * __uint_as_float(v[q2 * 8 + 2 * i]), p_hi * __uint_as_float(v[q2 * 8 + 2 * i + 1]));
+#endif
+                }
+                const uint4 o = make_uint4(o4[0], o4[1], o4[2], o4[3]);
                 const int chunk = chunk0 + hf * 2 + q2;
                 *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
                 dsp[q2 * 4 + 0] = o.x;
@@ -697,7 +711,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     tc_fence_before_sync();
     __syncthreads();
     if (warp == Cfg::kWarpMmaS) {
-        if (*abort_flag != 0) __nanosleep(20000);  // let in-flight copies and MMAs drain before TMEM is released
+        if (*abort_flag != 0) abort_grace_period();  // in-flight copies and MMAs land before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
 }

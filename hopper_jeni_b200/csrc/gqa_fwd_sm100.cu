@@ -123,7 +123,9 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 
     // ---- setup ------------------------------------------------------------------
     if (tid == 0) {
-        *abort_flag = 0;
+        // a non-zero status word (a bounded wait gave up earlier and nobody has read the report yet) makes
+        // every later thread block skip its work, so a wedged launch drains in one wave
+        *abort_flag = (*reinterpret_cast<volatile unsigned int*>(p.status) != 0u) ? 98u : 0u;
         for (int i = 0; i < 2; ++i) {
             mbar_init(&q_full[i], 1);
             mbar_init(&o_full[i], 1);
@@ -149,6 +151,10 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (*abort_flag != 0) {  // uniform: every thread reads the flag after the barrier
+        if (warp == kWarpMma0) tmem_dealloc(tmem, Cfg::kTmemCols);
+        return;
+    }
 
     if (warp == kWarpTma) {
         // ======================= TMA producer =======================
@@ -388,7 +394,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     tc_fence_before_sync();
     __syncthreads();
     if (warp == kWarpMma0) {
-        if (*abort_flag != 0) __nanosleep(20000);  // let in-flight copies and MMAs drain before TMEM is released
+        if (*abort_flag != 0) abort_grace_period();  // in-flight copies and MMAs land before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
 }
@@ -437,7 +443,6 @@ extern "C" int gqa_debug_copy_fwd_trace(long long* host) {
 
 int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
                      unsigned int* status, cudaStream_t stream) {
-    GQA_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(unsigned int), stream));
     if (s.D == 64) return launch_fwd_t<64>(Q, K, V, O, LSE, s, status, stream);
     return launch_fwd_t<128>(Q, K, V, O, LSE, s, status, stream);
 }

@@ -146,6 +146,12 @@ int make_col8_3_tmap(CUtensorMap* out, const void* base, uint64_t S, uint64_t n_
     return make_tmap3(out, base, 8, S, n_outer, S * 8, 8u, box_rows, 5u);
 }
 
+// Status word of the forward kernels: a fixed device array (no allocation), one per GPU that loads the library.
+// Reports are sticky: a kernel writes the word only while it is zero, no launch clears it, and
+// gqa_check_status(NULL, ...) clears it after reading, so forwards on different streams cannot erase each
+// other's report.  Until it has been read, later forward launches on that device return without computing.
+static __device__ __align__(256) unsigned int g_forward_status[64];
+
 int forward_status_word(unsigned int** out) {
     constexpr int kMaxDev = 64;
     static unsigned int* words[kMaxDev] = {};
@@ -155,10 +161,11 @@ int forward_status_word(unsigned int** out) {
     if (dev < 0 || dev >= kMaxDev) return GQA_ERR_BAD_ARGUMENT;
     std::lock_guard<std::mutex> lock(mu);
     if (!words[dev]) {
-        unsigned int* p = nullptr;
-        GQA_CUDA_TRY(cudaMalloc(&p, 256));
-        GQA_CUDA_TRY(cudaMemset(p, 0, 256));
-        words[dev] = p;
+        // in host code the array's name is a handle for the runtime, not an address a kernel can use
+        void* p = nullptr;
+        GQA_CUDA_TRY(cudaGetSymbolAddress(&p, g_forward_status));
+        if (!p) return GQA_ERR_CUDA;
+        words[dev] = static_cast<unsigned int*>(p);
     }
     *out = words[dev];
     return GQA_OK;

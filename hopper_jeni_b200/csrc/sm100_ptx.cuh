@@ -60,15 +60,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Returns true when the phase with the given parity has completed.
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, uint32_t where) {
+// Returns true when the phase with the given parity has completed; gives up after `limit` SM cycles.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, uint32_t where,
+                                                   long long limit) {
     const long long t0 = clock64();
     uint32_t polls = 0;
     for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((++polls & 0x3ffu) == 0) {
             if (*ctx.cta_flag != 0) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit) {
                 *ctx.cta_flag = where;
                 atomicCAS(ctx.status, 0u, 0x80000000u | (where << 20) | (blockIdx.x & 0xfffffu));
                 return false;
@@ -78,7 +79,20 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, uint32_t where) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, ctx, where);
+    return mbar_wait_slow(bar, parity, ctx, where, kWaitLimitCycles);
+}
+// Same wait with a caller-chosen limit (the time-out self test runs the give-up path with a short one).
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, uint32_t where,
+                                                long long limit) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, ctx, where, limit);
+}
+
+// What a CTA does once its abort flag is set and every role has left its loop: copies and MMAs that were
+// issued before the give-up may still be in flight and write shared memory or TMEM, so the CTA idles for
+// about a millisecond (far longer than any of them takes) before it frees TMEM and exits.
+__device__ __forceinline__ void abort_grace_period() {
+    for (int i = 0; i < 4; ++i) __nanosleep(250000);
 }
 
 // ----------------------------------------------------------------------------

@@ -2,7 +2,8 @@
 // 128-byte-swizzled panels (by TMA or by hand), runs a 128 x N x 128 UMMA product in one of the
 // operand arrangements the attention kernels use and writes the fp32 result.  It exercises exactly
 // the descriptor helpers of sm100_ptx.cuh.
-#include "gqa_common.cuh"
+#include "../../include/gqa_selftest.h"
+#include "selftest_common.cuh"
 #include "sm100_ptx.cuh"
 
 namespace {
@@ -191,11 +192,11 @@ extern "C" int gqa_selftest_umma(const void* X, const void* Y, float* C, int N, 
     if ((N != 64 && N != 128) || mode < 0 || mode > 6) return GQA_ERR_UNSUPPORTED;
     if (!gqa::aligned16(X) || !gqa::aligned16(Y) || !gqa::aligned16(C)) return GQA_ERR_BAD_ARGUMENT;
     unsigned int* status = nullptr;
-    int rc = gqa::forward_status_word(&status);
+    int rc = gqa_selftest::status_area(&status);
     if (rc) return rc;
     rc = run_selftest(X, Y, C, N, mode, use_tma, 1, 0, nullptr, status, stream);
     if (rc) return rc;
-    return gqa_check_status(nullptr, stream_);
+    return gqa_check_status(status, stream_);
 }
 
 // Issue-rate probe for arrangements 0-5: `reps` x 8 back-to-back K = 16 products accumulating into one
@@ -204,17 +205,18 @@ extern "C" int gqa_selftest_umma(const void* X, const void* Y, float* C, int N, 
 extern "C" int gqa_selftest_umma_cycles(const void* X, const void* Y, float* C, int N, int mode, int reps,
                                         int two_issuers, float* cycles_per_product, gqa_stream_t stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    if (!X || !Y || !C || !cycles_per_product || reps < 1) return GQA_ERR_BAD_ARGUMENT;
+    // one CTA runs reps x 8 products back to back with no wait inside the loop: keep it to a few milliseconds
+    if (!X || !Y || !C || !cycles_per_product || reps < 1 || reps > 65536) return GQA_ERR_BAD_ARGUMENT;
     if ((N != 64 && N != 128) || mode < 0 || mode > 5) return GQA_ERR_UNSUPPORTED;
     unsigned int* status = nullptr;
-    int rc = gqa::forward_status_word(&status);
+    int rc = gqa_selftest::status_area(&status);
     if (rc) return rc;
-    long long* dcycles = reinterpret_cast<long long*>(status + 2);  // the status allocation is 256 bytes
+    long long* dcycles = reinterpret_cast<long long*>(status + 2);  // the status area is 256 bytes
     rc = run_selftest(X, Y, C, N, mode, 1, reps, two_issuers ? 1 : 0, dcycles, status, stream);
     if (rc) return rc;
     long long h[2] = {0, 0};
     GQA_CUDA_TRY(cudaMemcpyAsync(h, dcycles, sizeof h, cudaMemcpyDeviceToHost, stream));
     GQA_CUDA_TRY(cudaStreamSynchronize(stream));
     *cycles_per_product = (float)(h[0] > h[1] ? h[0] : h[1]) / (8.0f * reps);
-    return gqa_check_status(nullptr, stream_);
+    return gqa_check_status(status, stream_);
 }

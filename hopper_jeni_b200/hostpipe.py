@@ -76,4 +76,7 @@ class HostBackward:
         cur.wait_stream(self.s_out)
 
     def synchronize(self):
+        """Wait for the last device->host copy, then raise if a bounded device-side wait gave up in any chunk."""
         self.s_out.synchronize()
+        for slot in self.slots:
+            ops.check_status(slot["ws"], stream=self.s_run)

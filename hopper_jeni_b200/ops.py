@@ -28,6 +28,17 @@ def _req(t: torch.Tensor, name: str, dtype) -> None:
         raise ValueError(f"{name} must be contiguous")
 
 
+def _req_like(t: torch.Tensor, name: str, like: torch.Tensor, shape=None, dtype=None) -> None:
+    """`t` must live on `like`'s device, be contiguous and have exactly the given shape and dtype: the C ABI
+    receives raw pointers, so a wrong-sized or wrong-device tensor would become an out-of-bounds access."""
+    _req(t, name, like.dtype if dtype is None else dtype)
+    if t.device != like.device:
+        raise ValueError(f"{name} is on {t.device}, expected {like.device}")
+    want = tuple(like.shape if shape is None else shape)
+    if tuple(t.shape) != want:
+        raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {want}")
+
+
 def _dims(q, k, layout="bhsd"):
     if layout == "bshd":
         B, S, Hq, D = q.shape
@@ -58,8 +69,9 @@ def gqa_forward(q, k, v, causal: bool = False, scale: float | None = None, out=N
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
     out = torch.empty_like(q) if out is None else out
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device) if lse is None else lse
-    _req(out, "O", torch.bfloat16)
-    _req(lse, "LSE", torch.float32)
+    _req_like(v, "V", k)
+    _req_like(out, "O", q)
+    _req_like(lse, "LSE", q, shape=(B, Hq, S), dtype=torch.float32)
     with torch.cuda.device(q.device):
         rc = lib.gqa_fwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                             B, Hq, Hkv, S, D, int(bool(causal)), scale, _stream_ptr(stream),
@@ -92,6 +104,15 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
+    _req_like(v, "V", k)
+    for t, n in ((o, "O"), (do, "dO"), (dq, "dQ")):
+        _req_like(t, n, q)
+    for t, n in ((dk, "dK"), (dv, "dV")):
+        _req_like(t, n, k)
+    _req_like(lse, "LSE", q, shape=(B, Hq, S), dtype=torch.float32)
+    if (not workspace.is_cuda or workspace.device != q.device or not workspace.is_contiguous()
+            or workspace.numel() * workspace.element_size() < need):
+        raise ValueError(f"workspace must be contiguous memory on {q.device} of at least {need} bytes")
     with torch.cuda.device(q.device):
         args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,
@@ -142,8 +163,8 @@ def check_status(workspace=None, stream=None) -> None:
 
 
 def checker_forward(q, k, v, causal=False, scale=None):
-    """CUDA-core checker forward (diagnostics; slow)."""
-    lib = capi.load_library()
+    """CUDA-core checker forward (diagnostics library; slow)."""
+    lib = capi.load_selftest_library()
     B, Hq, Hkv, S, D = _dims(q, k)
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
     out = torch.empty_like(q)
@@ -155,8 +176,8 @@ def checker_forward(q, k, v, causal=False, scale=None):
 
 
 def checker_backward(q, k, v, o, do, lse, causal=False, scale=None):
-    """CUDA-core checker backward (diagnostics; slow)."""
-    lib = capi.load_library()
+    """CUDA-core checker backward (diagnostics library; slow)."""
+    lib = capi.load_selftest_library()
     B, Hq, Hkv, S, D = _dims(q, k)
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -169,8 +190,8 @@ def checker_backward(q, k, v, o, do, lse, causal=False, scale=None):
 
 
 def selftest_umma(x, y, n: int, mode: int, use_tma: bool):
-    """Run the UMMA building-block self test; returns C [128, n] fp32."""
-    lib = capi.load_library()
+    """Run the UMMA building-block self test (diagnostics library); returns C [128, n] fp32."""
+    lib = capi.load_selftest_library()
     c = torch.empty((128, n), dtype=torch.float32, device=x.device)
     rc = lib.gqa_selftest_umma(x.data_ptr(), y.data_ptr(), c.data_ptr(), n, mode, int(use_tma), _stream_ptr())
     capi.check("gqa_selftest_umma", rc)

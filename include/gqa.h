@@ -10,8 +10,8 @@
  * Supported: D in {64, 128}, any S >= 1 (the reference needs S % 64 == 0 in the backward,
  * src/attention/GQA_bwd_baseline.cu:549-602, and S % 256 == 0 in the forward,
  * src/attention/GQA_fwd_ref.cu:352; here a partial last tile is masked), Hq a multiple of Hkv,
- * all pointers 16-byte aligned.  Anything else returns an error code; the library
- * never exits the process and never traps the device.
+ * all pointers 16-byte aligned, scale finite and > 0.  Anything else returns an error code; the
+ * library never exits the process and never traps the device.
  *
  * All functions return GQA_OK (0) or a negative gqa_status.  Work is enqueued
  * on `stream`; the functions do not synchronise it unless stated.
@@ -30,7 +30,7 @@ typedef struct CUstream_st* gqa_stream_t; /* same handle as cudaStream_t */
 
 typedef enum gqa_status {
     GQA_OK = 0,
-    GQA_ERR_BAD_ARGUMENT = -1,   /* null pointer, non-positive size, misaligned pointer */
+    GQA_ERR_BAD_ARGUMENT = -1,   /* null pointer, non-positive size, misaligned pointer, scale not finite or <= 0 */
     GQA_ERR_UNSUPPORTED = -2,    /* shape outside the supported set (D in {64,128}, Hq % Hkv == 0) */
     GQA_ERR_WORKSPACE = -3,      /* workspace missing or smaller than gqa_bwd_workspace_bytes() */
     GQA_ERR_CUDA = -4,           /* a CUDA runtime/driver call failed (see gqa_last_cuda_error) */
@@ -83,7 +83,8 @@ size_t gqa_bwd_workspace_bytes(int B, int Hq, int Hkv, int S, int D, int causal)
  * launcher in src/attention/GQA_bwd.cu).  G is derived as Hq / Hkv.
  * `workspace` must be 256-byte aligned device memory of at least
  * gqa_bwd_workspace_bytes(...) bytes; calls that share a workspace must not overlap.
- * dK and dV are bit-reproducible from run to run; dQ is accumulated with fp32 atomics.
+ * dK and dV are bit-reproducible from run to run; dQ is summed over the KV tiles by fp32 TMA reduce-add
+ * operations at L2 whose order varies from run to run (see GQA_BWD_DETERMINISTIC below).
  */
 int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO,
             const float* LSE, void* dQ, void* dK, void* dV,
@@ -97,7 +98,7 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
  * is bit-reproducible from run to run as dK and dV always are.  The reference's dQ path is order-dependent
  * (cp.reduce.async.bulk add, src/attention/GQA_bwd_baseline.cu:360-365, run-to-run differences noted in
  * docs/report.md:115-116) and has no such switch; its determinism probe
- * (src/attention/vj1d_determinism_probe.cu:33) is what this mode is checked with.  Slower than the default
+ * (precision/vj1d_determinism_probe.cu:33) is what this mode is checked with.  Slower than the default
  * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.
  * GQA_LAYOUT_BSHD (see gqa_fwd_ex): Q, O, dO, dQ are [B,S,Hq,D] and K, V, dK, dV [B,S,Hkv,D]; LSE stays [B,Hq,S].
  * Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
@@ -163,8 +164,15 @@ int gqa_bwd_delta(const void* O, const void* dO, float* delta, size_t rows, int 
 
 /*
  * Reads the status word a previous gqa_fwd/gqa_bwd left on the device and returns
- * GQA_OK or GQA_ERR_DEVICE_TIMEOUT.  Synchronises `stream`.  For gqa_bwd pass the
- * same workspace; for gqa_fwd pass NULL (the forward uses a library-owned word).
+ * GQA_OK or GQA_ERR_DEVICE_TIMEOUT (which wait gave up, in which thread block: gqa_last_cuda_error()).
+ * Synchronises `stream`.  For gqa_bwd pass the same workspace (its first word is the status word, cleared
+ * at the start of every gqa_bwd call).  For gqa_fwd pass NULL: the forward reports into a 256-byte
+ * device array that is part of the library, one per GPU, no allocation.  That report is sticky, like a
+ * CUDA error: no launch clears it, so forwards running on several streams cannot erase each other's
+ * report, and while it is set every later gqa_fwd on that GPU returns without computing (its thread
+ * blocks exit at once).  Reading it with this function clears it.  In both kernels a thread block that
+ * starts after another one has given up exits immediately, so a wedged launch drains within one wave.
+ * The reference has no such path: its waits spin without limit (src/attention/GQA_bwd_baseline.cu:85-93).
  */
 int gqa_check_status(const void* workspace, gqa_stream_t stream);
 
@@ -179,50 +187,6 @@ unsigned long long gqa_launch_count(void);
 
 /* Library version, "major.minor". */
 const char* gqa_version(void);
-
-/*
- * Building-block self test: one 128 x N x 128 bf16 UMMA product from two
- * 128 x 128 bf16 matrices X and Y (row-major) into C[128, N] fp32.
- *   mode 0: C = X  * Y^T   (A K-major,  B K-major)
- *   mode 1: C = X  * Y     (A K-major,  B MN-major)
- *   mode 2: C = X^T * Y^T  (A MN-major, B K-major)
- *   mode 3: C = X^T * Y    (A MN-major, B MN-major)
- *   mode 4: C = X  * Y^T   (A from tensor memory, B K-major)
- *   mode 5: C = X  * Y     (A from tensor memory, B MN-major)
- *   mode 6: C = X  * Y^T + X[:, :16] * Y[:, :16]^T  (mode 0 plus one K step read through
- *           un-swizzled 16-byte-row column panels)
- * N is 64 or 128 (for N = 64 only the first 64 rows/columns of Y are used).
- * use_tma != 0 stages X and Y with TMA tile loads, otherwise threads write the
- * swizzled layout themselves.  Synchronises `stream`.  No counterpart in the
- * reference (its kernels are wgmma-based); used by the test-suite only.
- */
-int gqa_selftest_umma(const void* X, const void* Y, float* C, int N, int mode, int use_tma,
-                      gqa_stream_t stream);
-
-/*
- * Issue-rate probe over arrangements 0-5: reps x 8 back-to-back K = 16 products into one
- * accumulator, issued by one warp or (two_issuers != 0) by two warps on separate accumulators;
- * *cycles_per_product (host memory) receives the SM cycles per product per issuing warp.
- * C is scratch.  Synchronises `stream`.  No counterpart in the reference.
- */
-int gqa_selftest_umma_cycles(const void* X, const void* Y, float* C, int N, int mode, int reps,
-                             int two_issuers, float* cycles_per_product, gqa_stream_t stream);
-
-/*
- * CUDA-core checker kernels (diagnostics): a slow, simple restatement of forward
- * and backward on the device, used by the tests to cross-check the tensor-core
- * kernels at sizes where the CPU oracle takes too long.  No product entry point
- * dispatches to them.  Same tensor contract as above, any S, D <= 128;
- * `delta_scratch` is B*Hq*S floats of device memory.  They follow the reference's
- * per-head loops (precision/baseline_gqa.py:169-197).
- */
-int gqa_checker_fwd_simt(const void* Q, const void* K, const void* V, void* O, float* LSE,
-                         int B, int Hq, int Hkv, int S, int D, int causal, float scale,
-                         gqa_stream_t stream);
-int gqa_checker_bwd_simt(const void* Q, const void* K, const void* V, const void* O, const void* dO,
-                         const float* LSE, void* dQ, void* dK, void* dV, float* delta_scratch,
-                         int B, int Hq, int Hkv, int S, int D, int causal, float scale,
-                         gqa_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -37,3 +37,11 @@ def gqa_lib():
     from hopper_jeni_b200 import capi
 
     return capi.load_library()
+
+
+@pytest.fixture(scope="session")
+def selftest_lib(gqa_lib):
+    """The diagnostics library (checker kernels, building-block and time-out self tests)."""
+    from hopper_jeni_b200 import capi
+
+    return capi.load_selftest_library()

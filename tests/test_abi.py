@@ -11,19 +11,24 @@ from hopper_jeni_b200 import capi
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "gqa.h")).read()
+def _declared_symbols(header="gqa.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(gqa_[a-z0-9_]+|launch_gqa)\s*\(", text)))
 
 
 def test_header_and_binding_agree():
     assert _declared_symbols() == sorted(capi.EXPORTS)
+    assert _declared_symbols("gqa_selftest.h") == sorted(capi.SELFTEST_EXPORTS)
+    assert not set(capi.EXPORTS) & set(capi.SELFTEST_EXPORTS)
 
 
-def test_library_exports_every_declared_symbol(gqa_lib):
+def test_library_exports_every_declared_symbol(gqa_lib, selftest_lib):
     for name in _declared_symbols():
         assert hasattr(gqa_lib, name), name
+    for name in _declared_symbols("gqa_selftest.h"):
+        assert hasattr(selftest_lib, name), name
+        assert not hasattr(gqa_lib, name), f"{name}: diagnostics must not be exported by the product library"
 
 
 def test_version_and_status_strings(gqa_lib):
@@ -45,7 +50,7 @@ def test_workspace_bytes_formula(gqa_lib):
     assert gqa_lib.gqa_bwd_workspace_bytes(B, 10, 4, S, D, 0) == 0
 
 
-def test_argument_validation_needs_no_device(gqa_lib):
+def test_argument_validation_needs_no_device(gqa_lib, selftest_lib):
     p = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
     assert gqa_lib.gqa_fwd(None, p, p, p, None, 1, 4, 2, 128, 64, 0, 0.125, None) == -1
     assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 0, 64, 0, 0.125, None) == -1        # S <= 0
@@ -57,7 +62,13 @@ def test_argument_validation_needs_no_device(gqa_lib):
     assert gqa_lib.gqa_bwd(p, p, p, p, p, p, p, p, p, 1, 4, 2, 128, 64, 0, 0.125, None, 0, None) == -3
     assert gqa_lib.gqa_bwd(p, p, p, p, p, p, p, p, p, 1, 4, 2, 128, 64, 0, 0.125, p, 16, None) == -3
     assert gqa_lib.gqa_bwd(p, p, p, p, p, None, p, p, p, 1, 4, 2, 128, 64, 0, 0.125, p, 1 << 30, None) == -1
-    assert gqa_lib.gqa_selftest_umma(p, p, p, 96, 0, 0, None) == -2
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 128, 64, 0, 0.0, None) == -1        # scale must be > 0
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 128, 64, 0, float("inf"), None) == -1
+    assert gqa_lib.gqa_bwd(p, p, p, p, p, p, p, p, p, 1, 4, 2, 128, 64, 0, -0.125, p, 1 << 30, None) == -1
+    assert selftest_lib.gqa_selftest_umma(p, p, p, 96, 0, 0, None) == -2
+    assert selftest_lib.gqa_selftest_umma_cycles(p, p, p, 128, 0, 1 << 20, 0, None, None) == -1  # reps capped
+    assert selftest_lib.gqa_selftest_timeout(p, 10 ** 10, 1, None) == -1                           # limit capped
+    assert selftest_lib.gqa_selftest_timeout(None, 1000, 1, None) == -1
     assert gqa_lib.gqa_bwd_delta(p, p, p, 16, 32, None) == -2
 
 

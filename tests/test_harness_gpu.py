@@ -35,3 +35,12 @@ def test_cpp_harness_gates_against_fp32_sdpa(gqa_lib, tmp_path, dims):
     (dv + 1.0).astype(np.float32).tofile(os.path.join(data, "gqa_dv.bin"))
     bad = _run(dims, data)
     assert bad.returncode == 4, bad.returncode
+
+
+def test_cpp_harness_synthetic_mode_reports_no_gate(gqa_lib):
+    """Without golden files nothing is compared: the JSON line must say so (gate_pass null, no rel_rms)."""
+    out = subprocess.run([BENCH, "1", "4", "2", "256", "64", "0", "--synthetic", "--iters", "2", "--warmup", "1",
+                          "--runs", "1"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    line = json.loads([l for l in out.stdout.splitlines() if l.startswith('{"harness"')][-1])
+    assert line["gate_pass"] is None and "rel_rms" not in line and line["outputs_finite"] is True

@@ -37,7 +37,7 @@ def test_umma_product(gqa_lib, mode, n, use_tma):
     np.testing.assert_allclose(util.to_np(c), want, rtol=1e-4, atol=1e-3)
 
 
-def test_issue_rate_probe(gqa_lib):
+def test_issue_rate_probe(selftest_lib):
     """A lean warp-uniform issue loop keeps the tensor pipe busy: 128x128x16 products complete every
     ~64 cycles from one issuing warp, and two issuing warps share that rate (each sees ~128)."""
     import ctypes
@@ -48,7 +48,7 @@ def test_issue_rate_probe(gqa_lib):
     out = {}
     for two in (0, 1):
         cy = ctypes.c_float()
-        rc = gqa_lib.gqa_selftest_umma_cycles(x.data_ptr(), y.data_ptr(), c.data_ptr(), 128, 0, 64, two,
+        rc = selftest_lib.gqa_selftest_umma_cycles(x.data_ptr(), y.data_ptr(), c.data_ptr(), 128, 0, 64, two,
                                               ctypes.byref(cy), None)
         assert rc == 0
         out[two] = cy.value

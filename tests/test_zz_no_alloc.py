@@ -42,14 +42,20 @@ def test_static_scratch_backward_matches_gqa_bwd_twice(gqa_lib, shape, causal):
         dk = torch.full_like(tk, float("nan"))
         dv = torch.full_like(tv, float("nan"))
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        # Device-wide free memory as the driver reports it: unlike torch's allocator statistics it also sees
+        # a cudaMalloc made inside the library.  Nothing else allocates between the two readings (the call
+        # takes raw pointers; the first call's address look-up of the scratch array allocates nothing).
+        free_before, _ = torch.cuda.mem_get_info()
         rc = _call_static(gqa_lib, tq, tk, tv, o, tdo, lse, dq, dk, dv, causal, sc)
         capi.check("gqa_bwd_static_scratch", rc)
         torch.cuda.synchronize()
-        # no growth of the torch allocator around the call (it may shrink: Python can free earlier temporaries)
-        assert torch.cuda.memory_allocated() <= before
+        free_after, _ = torch.cuda.mem_get_info()
+        # Checked on the second call: the first one may make the driver load the library's device code and the
+        # scratch array itself onto the GPU (lazy module loading), which is not an allocation made by the call.
+        if call == 1:
+            assert free_after >= free_before, f"device memory shrank by {free_before - free_after} bytes during the call"
         # dK and dV have one writer per element in both entry points: identical bits.  dQ is summed with
-        # fp32 atomics in an order that changes from run to run: the bf16 parity tolerance applies.
+        # fp32 reductions at L2 in an order that changes from run to run: the bf16 parity tolerance applies.
         assert torch.equal(dk, dk_ref) and torch.equal(dv, dv_ref)
         util.assert_close_bf16(util.to_np(dq), util.to_np(dq_ref), "dQ", util.REL_RMS_BWD)
 
