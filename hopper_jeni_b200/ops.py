@@ -110,9 +110,9 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
     for t, n in ((dk, "dK"), (dv, "dV")):
         _req_like(t, n, k)
     _req_like(lse, "LSE", q, shape=(B, Hq, S), dtype=torch.float32)
-    if (not workspace.is_cuda or workspace.device != q.device or not workspace.is_contiguous()
-            or workspace.numel() * workspace.element_size() < need):
-        raise ValueError(f"workspace must be contiguous memory on {q.device} of at least {need} bytes")
+    # its size is checked by the library (GQA_ERR_WORKSPACE, with the needed size in the error text)
+    if not workspace.is_cuda or workspace.device != q.device or not workspace.is_contiguous():
+        raise ValueError(f"workspace must be contiguous memory on {q.device}")
     with torch.cuda.device(q.device):
         args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,

@@ -1,8 +1,11 @@
 """The reference side of the config-size parity tests: PyTorch fp32 scaled_dot_product_attention and its
 autograd (the reference's own oracle call, precision/baseline_gqa.py:64-66, :429-435;
 harness/run_gqa_bwd_v44_bench.py:108-118) on the same bf16-rounded inputs, evaluated on the GPU in slices
-of (batch, KV-head) groups so that the fp32 score blocks of the long configs fit.  Test infrastructure
-only: nothing in the package imports it.
+of (batch, KV-head) groups so that the fp32 score blocks of the long configs fit.
+
+Test infrastructure: only tests/ and the checker legs of bench.py (outside every timed region) import it;
+nothing in the package does.  tests/test_sdpa_ref.py pins it to the C oracle, which is pinned to the reference's
+own fp64 loops by the golden fixtures.
 """
 from __future__ import annotations
 
@@ -64,6 +67,36 @@ def sdpa_group(q, k, v, do, scale, causal, want_lse=True):
         if want_lse:
             lse[h0:h0 + step] = lse_slice(q[h0:h0 + step].float(), kf, scale, causal)
     return o, lse, dq, dk, dv
+
+
+@torch.no_grad()
+def backward_given_o(q, k, v, o, do, scale, causal):
+    """fp32 backward of ONE (batch, KV-head) group that takes O as an INPUT, the way the operator does
+    (Delta = rowsum(dO * O) from the O it is handed: src/attention/GQA_bwd_baseline.cu:273-298), with every
+    other step exact: P = softmax(scale Q K^T), dP = dO V^T, dS = P (dP - Delta), dQ = scale dS K,
+    dK = scale dS^T Q, dV = P^T dO (precision/baseline_gqa.py:169-197).  With O in fp32 this is SDPA autograd; with
+    the bf16 O the operator really receives, it isolates the error that the input rounding of O alone puts
+    into dQ/dK -- which dominates for inputs like U[0,1), where Delta is a large common offset of dP.
+    q, o, do [G, S, D]; k, v [S, D].  Returns fp32 dq [G,S,D], dk [S,D], dv [S,D]."""
+    _no_tf32()
+    G, S, D = q.shape
+    kf, vf = k.float(), v.float()
+    dq = torch.empty(G, S, D, dtype=torch.float32, device=q.device)
+    dk = torch.zeros(S, D, dtype=torch.float32, device=q.device)
+    dv = torch.zeros_like(dk)
+    mask = torch.ones(S, S, dtype=torch.bool, device=q.device).triu_(1) if causal else None
+    for h in range(G):
+        qf, dof = q[h].float(), do[h].float()
+        s = torch.matmul(qf, kf.t()) * scale
+        if causal:
+            s.masked_fill_(mask, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        delta = (dof * o[h].float()).sum(-1, keepdim=True)
+        ds = p * (torch.matmul(dof, vf.t()) - delta)
+        dq[h] = torch.matmul(ds, kf) * scale
+        dk += torch.matmul(ds.t(), qf) * scale
+        dv += torch.matmul(p.t(), dof)
+    return dq, dk, dv
 
 
 def metrics(got: torch.Tensor, ref: torch.Tensor, atol=2e-2, rtol=2e-2):

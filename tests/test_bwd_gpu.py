@@ -52,15 +52,32 @@ def test_backward_matches_oracle(gqa_lib, oracle, shape, causal):
 def test_backward_matches_golden(gqa_lib, oracle, name):
     g = util.load_golden(name)
     dq, dk, dv = _run_bwd(g["q"], g["k"], g["v"], g["do"], g["causal"], g["scale"], oracle=oracle)
-    # U[0,1) inputs (the reference generator's distribution) make dP - Delta cancel to about 1 % of its
-    # operands, so the bf16 rounding of P and dS is amplified in dQ and dK; the reference's own
-    # element-wise gate still holds, the relative-RMS bound is widened for that fixture only.
+    # U[0,1) inputs (the reference generator's distribution): dP is Delta plus a fluctuation about half its size,
+    # and the backward is handed O rounded to bf16, so Delta = rowsum(dO * O) carries a row-coherent error that
+    # moves dQ by 2.7 % at this fixture in exact arithmetic (10 % at S = 4096; see test_config_parity_gpu.py).
+    # Against fp32 SDPA the reference's element-wise gate holds and the relative-RMS bound is widened for that
+    # fixture only; against the same fp32 backward given the same bf16 O the common bound holds (below).
     rel_rms = 6e-2 if "uniform" in name else util.REL_RMS_BWD
     for got, key in ((dq, "dq_fp32_sdpa"), (dk, "dk_fp32_sdpa"), (dv, "dv_fp32_sdpa")):
         util.assert_close_bf16(util.to_np(got), g[key], key, rel_rms)
     if g["causal"]:
         for got, key in ((dq, "dq_fp64"), (dk, "dk_fp64"), (dv, "dv_fp64")):
             util.assert_close_bf16(util.to_np(got), g[key], key, rel_rms)
+    # same inputs, O as the operator received it (bf16): every gradient within the common relative-RMS bound
+    from oracle import sdpa_ref
+
+    G = g["Hq"] // g["Hkv"]
+    o_ref, _ = oracle.forward(g["q"], g["k"], g["v"], g["causal"], g["scale"])
+    o_in = torch.from_numpy(util.bf16_round(o_ref))
+    tq, tk, tv, tdo = (torch.from_numpy(g[x]) for x in ("q", "k", "v", "do"))
+    for b in range(g["B"]):
+        for h in range(g["Hkv"]):
+            hs = slice(h * G, (h + 1) * G)
+            dq_o, dk_o, dv_o = sdpa_ref.backward_given_o(tq[b, hs], tk[b, h], tv[b, h], o_in[b, hs], tdo[b, hs],
+                                                         g["scale"], g["causal"])
+            util.assert_close_bf16(util.to_np(dq[b, hs]), dq_o.numpy(), "dQ given O", util.REL_RMS_BWD)
+            util.assert_close_bf16(util.to_np(dk[b, h]), dk_o.numpy(), "dK given O", util.REL_RMS_BWD)
+            util.assert_close_bf16(util.to_np(dv[b, h]), dv_o.numpy(), "dV given O", util.REL_RMS_BWD)
 
 
 @pytest.mark.parametrize("causal", [False, True])

@@ -13,7 +13,7 @@ import math
 import pytest
 import torch
 
-import sdpa_ref
+from oracle import sdpa_ref
 import util
 from hopper_jeni_b200 import ops
 
@@ -96,11 +96,22 @@ def test_forward_sweep_points(gqa_lib, S, D, causal):
     _parity(16, 16, 2, S, D, causal=causal, backward=False, groups=[(0, 0), (5, 1), (10, 0), (15, 1)])
 
 
-def test_reference_distribution_uniform_inputs(gqa_lib):
-    """The reference generator's own distribution (Q, K, V ~ U[0,1), dO ~ N(0,1); precision/baseline_gqa.py:400-402,
-    :422-423) at S = 4096, D = 128, causal, one of its sweep's head configurations (scripts/run_sweep.sh:17-18).
-    dP - Delta cancels to about 1 % of its operands here, which is where a second rounding of dS would show."""
-    B, Hq, Hkv, S, D = 2, 12, 4, 4096, 128
+# The reference's own sweep: B in {2,4,8} x (Hq,Hkv) in {(12,4),(16,4),(24,8),(32,8)}, S = 4096, D = 128, causal
+# (scripts/run_sweep.sh:17-18), inputs from its generator's distribution Q, K, V ~ U[0,1), dO ~ N(0,1)
+# (precision/baseline_gqa.py:400-402, :422-423).
+SWEEP = [(B, Hq, Hkv) for B in (2, 4, 8) for Hq, Hkv in ((12, 4), (16, 4), (24, 8), (32, 8))]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv", SWEEP)
+def test_reference_sweep_uniform_inputs(gqa_lib, B, Hq, Hkv):
+    """Two comparisons per tensor.  (1) Against fp32 SDPA autograd: the reference's own element-wise gate
+    |d| <= 2e-2 + 2e-2|ref| (src/attention/GQA_bwd_baseline.cu:677-679) must hold; the relative RMS of dQ is
+    reported, not bounded, because with these inputs it measures the INPUT contract, not the kernel: dP is
+    Delta plus a fluctuation about half its size, the backward receives O rounded to bf16, and that rounding
+    alone shifts Delta coherently along a row and moves dQ by about 10 % at S = 4096 in exact arithmetic
+    (2.7 % at S = 128; tests/test_sdpa_ref.py pins the restatement used to show it).  (2) Against the same fp32
+    backward handed the same bf16 O (the operator's contract): relative RMS <= 2e-2 for all three gradients."""
+    S, D, G = 4096, 128, Hq // Hkv
     sc = 1.0 / math.sqrt(D)
     g = torch.Generator(device="cuda").manual_seed(42)
     q = torch.rand(B, Hq, S, D, generator=g, device="cuda").bfloat16()
@@ -108,18 +119,23 @@ def test_reference_distribution_uniform_inputs(gqa_lib):
     v = torch.rand(B, Hkv, S, D, generator=g, device="cuda").bfloat16()
     do = torch.randn(B, Hq, S, D, generator=torch.Generator(device="cuda").manual_seed(43), device="cuda").bfloat16()
     o, lse = ops.gqa_forward(q, k, v, causal=True, scale=sc)
+    ops.check_status()
     ws = torch.empty(ops.bwd_workspace_bytes(B, Hq, Hkv, S, D, True), dtype=torch.uint8, device="cuda")
     dq, dk, dv = ops.gqa_backward(q, k, v, o, do, lse, causal=True, scale=sc, workspace=ws)
     ops.check_status(ws)
-    worst = {}
-    G = Hq // Hkv
+    vs_sdpa, vs_same_o = {}, {}
     for b in range(B):
         for h in range(Hkv):
             hs = slice(h * G, (h + 1) * G)
-            o_r, lse_r, dq_r, dk_r, dv_r = sdpa_ref.sdpa_group(q[b, hs], k[b, h], v[b, h], do[b, hs], sc, True)
-            _check("O", o[b, hs], o_r, util.REL_RMS_FWD, worst)
-            _check("dQ", dq[b, hs], dq_r, util.REL_RMS_BWD, worst)
-            _check("dK", dk[b, h], dk_r, util.REL_RMS_BWD, worst)
-            _check("dV", dv[b, h], dv_r, util.REL_RMS_BWD, worst)
-    print("\nuniform inputs: " + ", ".join(f"{n} max_abs {w['max_abs']:.3e} rel_rms {w['rel_rms']:.3e}"
-                                           for n, w in worst.items()))
+            o_r, _, dq_r, dk_r, dv_r = sdpa_ref.sdpa_group(q[b, hs], k[b, h], v[b, h], do[b, hs], sc, True, want_lse=False)
+            _check("O", o[b, hs], o_r, util.REL_RMS_FWD, vs_sdpa)
+            _check("dQ", dq[b, hs], dq_r, 1.0, vs_sdpa)          # element-wise gate only, see above
+            _check("dK", dk[b, h], dk_r, util.REL_RMS_BWD, vs_sdpa)
+            _check("dV", dv[b, h], dv_r, util.REL_RMS_BWD, vs_sdpa)
+            dq_o, dk_o, dv_o = sdpa_ref.backward_given_o(q[b, hs], k[b, h], v[b, h], o[b, hs], do[b, hs], sc, True)
+            _check("dQ", dq[b, hs], dq_o, util.REL_RMS_BWD, vs_same_o)
+            _check("dK", dk[b, h], dk_o, util.REL_RMS_BWD, vs_same_o)
+            _check("dV", dv[b, h], dv_o, util.REL_RMS_BWD, vs_same_o)
+    fmt = lambda d: ", ".join(f"{n} max_abs {w['max_abs']:.3e} rel_rms {w['rel_rms']:.3e}" for n, w in d.items())
+    print(f"\nuniform sweep B{B} Hq{Hq} Hkv{Hkv}: vs fp32 SDPA: {fmt(vs_sdpa)} | vs fp32 backward given the same bf16 O: "
+          f"{fmt(vs_same_o)}")

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-import sdpa_ref
+from oracle import sdpa_ref
 import util
 
 
@@ -25,6 +25,11 @@ def test_sliced_sdpa_reference_matches_oracle(oracle, causal):
         np.testing.assert_allclose(dq.numpy(), dq_ref[0, hs], atol=2e-5)
         np.testing.assert_allclose(dk.numpy(), dk_ref[0, h], atol=2e-5)
         np.testing.assert_allclose(dv.numpy(), dv_ref[0, h], atol=2e-5)
+        # the O-as-input restatement, given the exact O, is the same backward
+        dq2, dk2, dv2 = sdpa_ref.backward_given_o(tq[0, hs], tk[0, h], tv[0, h], o, tdo[0, hs], sc, causal)
+        np.testing.assert_allclose(dq2.numpy(), dq_ref[0, hs], atol=2e-5)
+        np.testing.assert_allclose(dk2.numpy(), dk_ref[0, h], atol=2e-5)
+        np.testing.assert_allclose(dv2.numpy(), dv_ref[0, h], atol=2e-5)
 
 
 def test_heads_per_slice_divides_the_group():
