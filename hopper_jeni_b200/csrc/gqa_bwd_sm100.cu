@@ -49,7 +49,7 @@ using namespace sm100;
 #ifndef GQA_BWD_TRACE_BLOCK
 #define GQA_BWD_TRACE_BLOCK 0
 #endif
-__device__ long long g_bwd_trace[3][64][4];
+__device__ long long g_bwd_trace[5][64][4];
 #define GQA_TRACE(role, it, slot)                                                                  \
     do {                                                                                           \
         if (blockIdx.x == GQA_BWD_TRACE_BLOCK && (it) < 64 && (threadIdx.x & 31) == 0) g_bwd_trace[role][it][slot] = clock64(); \
@@ -83,8 +83,11 @@ struct BwdCfg {
     // therefore pull the tile into registers as fast as TMEM delivers it (three 32-column chunks at once, the
     // fourth as soon as the first is staged) and hand the columns back before the copy engine has taken anything.
     static constexpr bool kDrainEarlyRelease = (D == 128);
-    static constexpr int kQStages = 2;
-    static constexpr int kDOStages = (D == 64) ? 2 : 1;
+    // Stages of the Q and dO rings.  A stage is released late in an iteration (Q by dK(it), dO by dV(it)) and a tile
+    // takes 1 000-1 700 cycles to arrive, so with two stages S^T(it+2) / dP^T(it+2) waited for their operands (seen on
+    // the clock64 timeline); D = 64 has the room for three.
+    static constexpr int kQStages = (D == 64) ? 3 : 2;
+    static constexpr int kDOStages = (D == 64) ? 3 : 1;
     static constexpr int kColPanel = kTile * 16;  // 128 rows x 16 B: an un-swizzled 8-column operand panel
     static constexpr int kDqBoxes = (D == 64) ? 2 : 1;  // 32-column fp32 boxes staged per drain round and warp
     static constexpr int kOffK = 0;
@@ -92,6 +95,8 @@ struct BwdCfg {
     static constexpr int kOffQ = kOffV + kTileBytes;
     static constexpr int kOffDO = kOffQ + kQStages * kTileBytes;
     static constexpr int kOffDS = kOffDO + kDOStages * kTileBytes;
+    // (a second dS^T staging buffer, dQ(it) reading one while dS^T(it+1) is written into the other, was measured
+    // at D = 64 and changed nothing)
     static constexpr int kOffDQ = kOffDS + 2 * kPanel;   // dQ staging: 4 drain warps x kDqBoxes x (32 rows x 128 B)
     static constexpr int kOffOnes = kOffDQ + 4 * kDqBoxes * 4096;   // constant A operand of the extra K step
     static constexpr int kOffLseCol = kOffOnes + kColPanel;         // [kQStages] -LSE/scale columns of the query tile
@@ -159,21 +164,24 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     uint8_t* sDltCol = smem + Cfg::kOffDltCol;
     uint8_t* sZero = smem + Cfg::kOffZero;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+    // Every group of products is followed by ONE commit (a commit is not free: it takes a slot in the tensor core's
+    // queue like a small product), to a barrier that serves all the consumers of that group; the barriers that
+    // release a Q or dO stage are kept per stage, so that the TMA producer, which lags by one use, can wait on them
+    // by parity like everybody else.
     uint64_t* kv_full = bars + 0;    // TMA: K and V tiles
-    uint64_t* s_full = bars + 1;     // issuer S   -> elementwise: S^T(it) complete
-    uint64_t* dp_full = bars + 2;    // issuer S   -> elementwise: dP^T(it) complete
-    uint64_t* p_ready = bars + 3;    // elementwise -> issuers: P^T(it) stored, S^T(it) consumed
-    uint64_t* ds_ready = bars + 4;   // elementwise -> issuers: dS^T(it) stored, dP^T(it) consumed
-    uint64_t* p_free = bars + 5;     // issuer dV  -> P^T(it) consumed
-    uint64_t* ds_free = bars + 6;    // issuers dK + dQ -> dS^T(it) consumed
-    uint64_t* dq_full = bars + 7;    // issuer dQ  -> drain warps
-    uint64_t* dq_empty = bars + 8;   // drain warps -> issuers: dQ columns free
-    uint64_t* acc_full = bars + 9;   // issuers dV + dK -> epilogue
-    uint64_t* q_full = bars + 10;                    // [kQStages] TMA: Q tile + LSE + Delta rows
-    uint64_t* q_empty = q_full + Cfg::kQStages;      // [kQStages] issuers S + dK
-    uint64_t* do_full = q_empty + Cfg::kQStages;     // [kDOStages] TMA: dO tile
-    uint64_t* do_empty = do_full + Cfg::kDOStages;   // [kDOStages] issuers S + dV
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(do_empty + Cfg::kDOStages);
+    uint64_t* p_ready = bars + 1;    // elementwise -> issuers: P^T(it) stored, S^T(it) consumed
+    uint64_t* ds_ready = bars + 2;   // elementwise -> issuers: dS^T(it) stored, dP^T(it) consumed
+    uint64_t* ds_free = bars + 3;    // after dQ(it) (covers dK(it), same thread): dS^T(it) consumed, dQ(it) complete
+    uint64_t* dq_empty = bars + 4;   // drain warps -> issuers: dQ columns free
+    uint64_t* acc_full = bars + 5;   // issuers dV + dK after their last products -> epilogue
+    uint64_t* s_full = bars + 6;                     // [kQStages] after S^T(it): -> elementwise
+    uint64_t* dk_done = s_full + Cfg::kQStages;      // [kQStages] after dK(it): Q stage free (S^T(it) finished long before),
+                                                     //            and the dS^T copy in the dP^T columns has been read
+    uint64_t* q_full = dk_done + Cfg::kQStages;      // [kQStages] TMA: Q tile + -LSE/scale columns
+    uint64_t* dp_full = q_full + Cfg::kQStages;      // [kDOStages] after dP^T(it): -> elementwise; dO stage read by dP^T
+    uint64_t* p_free = dp_full + Cfg::kDOStages;     // [kDOStages] after dV(it): P^T(it) consumed; dO stage read by dV
+    uint64_t* do_full = p_free + Cfg::kDOStages;     // [kDOStages] TMA: dO tile + -Delta columns
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(do_full + Cfg::kDOStages);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
     const int tid = threadIdx.x;
@@ -212,22 +220,20 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // start after it skip their work (see below), so a wedged launch drains in one wave
         *abort_flag = (*reinterpret_cast<volatile unsigned int*>(p.status) != 0u) ? 98u : 0u;
         mbar_init(kv_full, 1);
-        mbar_init(s_full, 1);
-        mbar_init(dp_full, 1);
         mbar_init(p_ready, Cfg::kEwThreads);
         mbar_init(ds_ready, Cfg::kEwThreads);
-        mbar_init(p_free, 1);
-        mbar_init(ds_free, 2);
-        mbar_init(dq_full, 1);
+        mbar_init(ds_free, 1);
         mbar_init(dq_empty, 128);
         mbar_init(acc_full, 2);
         for (int i = 0; i < Cfg::kQStages; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&dk_done[i], 1);
             mbar_init(&q_full[i], 1);
-            mbar_init(&q_empty[i], 2);
         }
         for (int i = 0; i < Cfg::kDOStages; ++i) {
+            mbar_init(&dp_full[i], 1);
+            mbar_init(&p_free[i], 1);
             mbar_init(&do_full[i], 1);
-            mbar_init(&do_empty[i], 2);
         }
         fence_mbar_init();
     }
@@ -271,7 +277,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 {
                     const int st = it % Cfg::kQStages;
                     const uint32_t use = it / Cfg::kQStages;
-                    if (use > 0 && !mbar_wait(&q_empty[st], (use - 1) & 1, ctx, 10)) break;
+                    // the stage's last reader is dK of its previous use
+                    if (use > 0 && !mbar_wait(&dk_done[st], (use - 1) & 1, ctx, 10)) break;
                     // the -LSE/scale columns of the tile ride with Q (both are operands of S^T)
                     mbar_expect_tx(&q_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
@@ -281,7 +288,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 {
                     const int st = it % Cfg::kDOStages;
                     const uint32_t use = it / Cfg::kDOStages;
-                    if (use > 0 && !mbar_wait(&do_empty[st], (use - 1) & 1, ctx, 11)) break;
+                    // the stage's readers are dP^T and dV of its previous use (neither implies the other)
+                    if (use > 0 && !(mbar_wait(&dp_full[st], (use - 1) & 1, ctx, 11) && mbar_wait(&p_free[st], (use - 1) & 1, ctx, 12))) break;
                     // the -Delta columns ride with dO (both are operands of dP^T)
                     mbar_expect_tx(&do_full[st], Cfg::kTileBytes + Cfg::kColPanel);
                     for (int pn = 0; pn < Cfg::kPanels; ++pn)
@@ -314,23 +322,25 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             const int qs = it % Cfg::kQStages, dos = it % Cfg::kDOStages;
             ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 21);
             if (ok && it > 0) ok = mbar_wait(p_ready, (it - 1) & 1, ctx, 22);                        // S^T columns read
-            if (ok && it > 0 && Cfg::kPAliasesS) ok = mbar_wait(p_free, (it - 1) & 1, ctx, 23);      // P^T consumed
+            if (ok && it > 0 && Cfg::kPAliasesS)                                                     // P^T consumed
+                ok = mbar_wait(&p_free[(it - 1) % Cfg::kDOStages], ((it - 1) / Cfg::kDOStages) & 1, ctx, 23);
             if (!ok) break;
             tc_fence_after_sync();
-            issue(Cfg::kColS, k_addr, q_addr + qs * Cfg::kTileBytes, smem_u32(sLseCol) + qs * Cfg::kColPanel);
-            umma_commit_pred(leader, s_full);
-            umma_commit_pred(leader, &q_empty[qs]);
             GQA_TRACE(1, it, 0);
+            issue(Cfg::kColS, k_addr, q_addr + qs * Cfg::kTileBytes, smem_u32(sLseCol) + qs * Cfg::kColPanel);
+            umma_commit_pred(leader, &s_full[qs]);
+            GQA_TRACE(1, it, 1);
             ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 24);
             if (ok && it > 0) ok = mbar_wait(ds_ready, (it - 1) & 1, ctx, 25);                       // dP^T columns read
             if (ok && it > 0 && Cfg::kDqAliasesDp) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);  // dQ drained
-            if (ok && it > 0 && Cfg::kDsInTmem) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 27);      // dK read dS^T
+            if (ok && it > 0 && Cfg::kDsInTmem)                                                      // dK read dS^T
+                ok = mbar_wait(&dk_done[(it - 1) % Cfg::kQStages], ((it - 1) / Cfg::kQStages) & 1, ctx, 27);
             if (!ok) break;
             tc_fence_after_sync();
+            GQA_TRACE(1, it, 2);
             issue(Cfg::kColDP, v_addr, do_addr + dos * Cfg::kTileBytes, smem_u32(sDltCol) + dos * Cfg::kColPanel);
-            umma_commit_pred(leader, dp_full);
-            umma_commit_pred(leader, &do_empty[dos]);
-            GQA_TRACE(1, it, 1);
+            umma_commit_pred(leader, &dp_full[dos]);
+            GQA_TRACE(1, it, 3);
         }
     } else if (warp == Cfg::kWarpMmaDV) {
         // ======================= issuer: dV += P^T dO(it)  (A from TMEM, B = dO read MN-major) =======================
@@ -342,14 +352,14 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 30) && mbar_wait(p_ready, it & 1, ctx, 31);
             if (!ok) break;
             tc_fence_after_sync();
+            GQA_TRACE(3, it, 0);
             const uint32_t b0 = do_addr + dos * Cfg::kTileBytes;
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk)
                 umma_ts_pred(leader, tmem + Cfg::kColDV, tmem + p_col_of_kstep<D>(kk),
                              make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
-            umma_commit_pred(leader, p_free);
-            umma_commit_pred(leader, &do_empty[dos]);
-            GQA_TRACE(1, it, 2);
+            umma_commit_pred(leader, &p_free[dos]);
+            GQA_TRACE(3, it, 1);
         }
         if (ok) umma_commit_pred(leader, acc_full);
     } else if (warp == Cfg::kWarpMmaDK) {
@@ -362,7 +372,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 32) && mbar_wait(ds_ready, it & 1, ctx, 33);
             if (!ok) break;
             tc_fence_after_sync();
+            GQA_TRACE(4, it, 0);
             const uint32_t b0 = q_addr + qs * Cfg::kTileBytes;
+            const uint32_t ds_buf = ds_addr;
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 if constexpr (Cfg::kDsInTmem)  // A = bf16 dS^T in the dP^T columns: query columns [16kk, 16kk+16)
@@ -370,23 +382,23 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                                  make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
                 else
                     umma_ss_pred(leader, tmem + Cfg::kColDK,
-                                 make_sdesc_sw128(ds_addr + (kk >> 2) * kPanel + (kk & 3) * 32, 16, 1024),
+                                 make_sdesc_sw128(ds_buf + (kk >> 2) * kPanel + (kk & 3) * 32, 16, 1024),
                                  make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
             }
-            umma_commit_pred(leader, ds_free);
-            umma_commit_pred(leader, &q_empty[qs]);
+            umma_commit_pred(leader, &dk_done[qs]);
+            GQA_TRACE(4, it, 1);
             {  // dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major)
                 if (it > 0) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 36);
                 if (!ok) break;
                 tc_fence_after_sync();
+                GQA_TRACE(4, it, 2);
                 const uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
-                    umma_ss_pred(leader, tmem + Cfg::kColDQ, make_sdesc_sw128(ds_addr + kk * 2048, kPanel, 1024),
+                    umma_ss_pred(leader, tmem + Cfg::kColDQ, make_sdesc_sw128(ds_buf + kk * 2048, kPanel, 1024),
                                  make_sdesc_sw128(k_addr + kk * 2048, kPanel, 1024), idesc_dq, kk > 0);
-                umma_commit_pred(leader, dq_full);
                 umma_commit_pred(leader, ds_free);
-                GQA_TRACE(1, it, 3);
+                GQA_TRACE(4, it, 3);
             }
         }
         if (ok) umma_commit_pred(leader, acc_full);
@@ -443,7 +455,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             bool turn_mine = (turn == nullptr);  // becomes true once this warp may reduce into the slice
             // first look at the counter now: its round trip to L2 hides behind the TMEM loads and the staging
             const unsigned int early = (turn && lane == 0) ? ld_acquire_gpu(turn) : 0xffffffffu;
-            if (!mbar_wait(dq_full, it & 1, ctx, 40)) break;
+            if (!mbar_wait(ds_free, it & 1, ctx, 40)) break;  // dQ(it) complete
             tc_fence_after_sync();
             GQA_TRACE(2, it, 0);
             constexpr int kRounds = D / (32 * Cfg::kDqBoxes);
@@ -537,7 +549,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         const uint32_t tDP = tmem + lane_addr + Cfg::kColDP + w * C;
         const uint32_t tP = tmem + lane_addr + (Cfg::kPAliasesS ? (Cfg::kColS + w * C) : (Cfg::kColP + w * (C / 2)));
         // dS^T row j, query columns [C*w, C*w+C): 64-column panel (C*w)/64, 16-byte chunks from ((C*w) % 64)/8 on
-        uint8_t* ds_row = sDS + ((w * C) >> 6) * kPanel + j * 128;
+        uint8_t* ds_row0 = sDS + ((w * C) >> 6) * kPanel + j * 128;
         const int chunk0 = ((w * C) & 63) >> 3;
         const float c = p.scale_log2;
         const bool trace_me = (warp == kWarpEw0);
@@ -566,7 +578,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         };
         // dS^T of 16 columns from the dP^T values v (which already hold dP - Delta) and the packed P^T pairs
         // -> two 16-byte chunks of the dS^T row (and the same packed values for the TMEM copy)
-        auto ds_half = [&](const uint32_t (&v)[16], int hf, const uint32_t* pk, uint32_t* dsp) {
+        auto ds_half = [&](const uint32_t (&v)[16], int hf, const uint32_t* pk, uint32_t* dsp, uint8_t* ds_row) {
 #pragma unroll
             for (int q2 = 0; q2 < 2; ++q2) {
                 const uint32_t* pp = pk + q2 * 4;
@@ -606,7 +618,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         };
 
         // ---- prologue: P^T(0)
-        ok = mbar_wait(s_full, 0, ctx, 51);
+        ok = mbar_wait(&s_full[0], 0, ctx, 51);
         if (ok) {
             tc_fence_after_sync();
             const bool masked0 = p.causal != 0;  // iteration 0 is the diagonal tile when causal
@@ -623,8 +635,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             const bool more = it + 1 < n_iter;
             const bool masked_next = p.causal && ((it + 1) % n_qt == 0);
             // ---- dS^T(it) from dP^T(it) and the P^T(it) kept in registers
-            ok = mbar_wait(dp_full, it & 1, ctx, 53);
-            if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 54);
+            ok = mbar_wait(&dp_full[it % Cfg::kDOStages], (it / Cfg::kDOStages) & 1, ctx, 53);
+            if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 54);  // dK(it-1) and dQ(it-1) have read dS^T(it-1)
             if (!ok) break;
             tc_fence_after_sync();
             if (trace_me) GQA_TRACE(0, it, 0);
@@ -635,7 +647,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     uint32_t vd[16];
                     tmem_ld16(tDP + hf * 16, vd);
                     tmem_wait_ld();
-                    ds_half(vd, hf, pk_cur + hf * 8, dsp + hf * 8);
+                    ds_half(vd, hf, pk_cur + hf * 8, dsp + hf * 8, ds_row0);
                 }
                 if constexpr (Cfg::kDsInTmem) {
                     static_assert(!Cfg::kDsInTmem || C == 32, "the TMEM copy of dS^T is written as one 16-column store");
@@ -652,7 +664,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             if (trace_me) GQA_TRACE(0, it, 1);
             if (!more) break;
             // ---- P^T(it+1) from S^T(it+1)
-            ok = mbar_wait(s_full, (it + 1) & 1, ctx, 51);
+            ok = mbar_wait(&s_full[(it + 1) % Cfg::kQStages], ((it + 1) / Cfg::kQStages) & 1, ctx, 51);
             if (!ok) break;
             tc_fence_after_sync();
             if (trace_me) GQA_TRACE(0, it, 2);
@@ -664,7 +676,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 p_half(vs, hf, masked_next, pk_cur + hf * 8);
             }
             if constexpr (!Cfg::kPAliasesS) {
-                ok = mbar_wait(p_free, it & 1, ctx, 52);  // dV(it) has consumed P^T(it): its columns can be rewritten
+                // dV(it) has consumed P^T(it): its columns can be rewritten
+                ok = mbar_wait(&p_free[it % Cfg::kDOStages], (it / Cfg::kDOStages) & 1, ctx, 52);
                 if (!ok) break;
                 tc_fence_after_sync();
             }

@@ -17,8 +17,6 @@
 //
 // Replaces gqa62::gqa_v62 / launch_gqa_v62 (src/attention/GQA_fwd_ref.cu:336-651):
 // same inputs/outputs, LSE = natural-log of the scaled-logit sum (:611-614).
-#include <cstdlib>
-
 #include "gqa_common.cuh"
 #include "gqa_kernels.cuh"
 #include "sm100_ptx.cuh"
@@ -445,11 +443,7 @@ extern "C" int gqa_debug_copy_fwd_trace(long long* host) {
 
 int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
                      unsigned int* status, cudaStream_t stream) {
-    if (s.D == 64) {
-        static const bool legacy = getenv("GQA_FWD64_LEGACY") != nullptr;  // A/B switch while the two are compared
-        return legacy ? launch_fwd_t<64>(Q, K, V, O, LSE, s, status, stream)
-                      : launch_fwd64_sm100(Q, K, V, O, LSE, s, status, stream);
-    }
+    if (s.D == 64) return launch_fwd_t<64>(Q, K, V, O, LSE, s, status, stream);
     return launch_fwd_t<128>(Q, K, V, O, LSE, s, status, stream);
 }
 

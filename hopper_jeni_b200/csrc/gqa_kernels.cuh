@@ -50,10 +50,6 @@ int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scal
 // Tensor-core forward (tcgen05 + TMEM + TMA).
 int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
                      unsigned int* status, cudaStream_t stream);
-// Tensor-core forward for D = 64: four softmax warpgroups per CTA, the keys of every block split between two
-// independent online-softmax streams per query tile that are merged in the epilogue.
-int launch_fwd64_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
-                       unsigned int* status, cudaStream_t stream);
 // Stage 2 of the backward: KV-tile-parallel main kernel (tcgen05 + TMEM + TMA); dK/dV written
 // once per element, dQ accumulated into dq_accum with fp32 reductions.
 // With dq_turn (zeroed counters, one per 32 query rows) the reductions of every dQ tile are applied in KV-tile
