@@ -28,7 +28,7 @@ bool scale_ok(float scale) { return scale > 0.f && scale < INFINITY; }
 
 int check_shape(int B, int Hq, int Hkv, int S, int D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0) return GQA_ERR_BAD_ARGUMENT;
-    if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
+    if (D < 8 || D > 128 || D % 8 != 0) return GQA_ERR_UNSUPPORTED;  // rows must be multiples of 16 bytes (TMA)
     if (Hq % Hkv != 0) return GQA_ERR_UNSUPPORTED;  // S may be any length: partial tiles are masked
     if ((size_t)B * Hq * S >= (size_t)1 << 31) return GQA_ERR_UNSUPPORTED;  // TMA row coordinate is 32-bit
     return GQA_OK;
@@ -44,6 +44,8 @@ int run_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, in
     if (!Q || !K || !V || !O || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
+    // [B,S,H,D]: a head's columns are followed by the next head's, so nothing reads as zero padding
+    if ((flags & GQA_LAYOUT_BSHD) && D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
     if (!gqa::aligned16(Q) || !gqa::aligned16(K) || !gqa::aligned16(V) || !gqa::aligned16(O) ||
         (LSE && !gqa::aligned16(LSE)))
         return GQA_ERR_BAD_ARGUMENT;
@@ -91,6 +93,7 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
     if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
+    if ((flags & GQA_LAYOUT_BSHD) && D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;  // see the forward
     const void* ptrs[] = {Q, K, V, O, dO, LSE, dQ, dK, dV};
     for (const void* p : ptrs)
         if (!gqa::aligned16(p)) return GQA_ERR_BAD_ARGUMENT;
@@ -124,7 +127,7 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
     rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[2], stream));
-    rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows() * (size_t)D, scale, stream, D, s.bshd ? S : 0, s.bshd ? Hq : 0);
+    rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows(), scale, stream, D, s.bshd ? S : 0, s.bshd ? Hq : 0);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[3], stream));
     return GQA_OK;

@@ -129,6 +129,7 @@ struct BwdParams {
     unsigned int* status;
     unsigned int* dq_turn;  // deterministic mode: one counter per 32 query rows (zeroed), else nullptr
     int Hq, Hkv, S, causal, n_tiles, G, bshd;
+    int d_real;  // head dimension of the tensors (<= D of the kernel; the columns beyond it read as zeros)
     float scale, scale_log2;
 };
 
@@ -695,7 +696,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             // element offset of this key row in dK / dV
             const size_t kv_pos = (size_t)kt * kTile + j;
             const size_t kv_elem = p.bshd ? (((size_t)b * p.S + kv_pos) * p.Hkv + hkv) * D
-                                          : (((size_t)b * p.Hkv + hkv) * p.S + kv_pos) * D;
+                                          : (((size_t)b * p.Hkv + hkv) * p.S + kv_pos) * p.d_real;
 #pragma unroll 1
             for (int which = 0; which < 2; ++which) {
                 const uint32_t tA = tmem + lane_addr + (which == 0 ? Cfg::kColDV : Cfg::kColDK) + w * kQuarter;
@@ -713,7 +714,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                         o.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * mul, __uint_as_float(v[8 * i + 3]) * mul);
                         o.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * mul, __uint_as_float(v[8 * i + 5]) * mul);
                         o.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * mul, __uint_as_float(v[8 * i + 7]) * mul);
-                        if (row_ok) *reinterpret_cast<uint4*>(dst + ch * 16 + i * 8) = o;
+                        if (row_ok && w * kQuarter + ch * 16 + i * 8 < p.d_real) *reinterpret_cast<uint4*>(dst + ch * 16 + i * 8) = o;
                     }
                 }
             }
@@ -736,7 +737,8 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     using Cfg = BwdCfg<D>;
     CUtensorMap mq, mk, mv, mdo;
     // see the coordinates in the kernel
-    const uint64_t S = s.S, qc = s.bshd ? (uint64_t)s.Hq * D : D, kc = s.bshd ? (uint64_t)s.Hkv * D : D;
+    // (the matrices are s.D columns wide; a box that reaches beyond them reads zeros there)
+    const uint64_t S = s.S, qc = s.bshd ? (uint64_t)s.Hq * D : s.D, kc = s.bshd ? (uint64_t)s.Hkv * D : s.D;
     const uint64_t nq = s.bshd ? s.B : (uint64_t)s.B * s.Hq, nkv = s.bshd ? s.B : (uint64_t)s.B * s.Hkv;
     const uint64_t nws = (uint64_t)s.B * s.Hq;
     int rc = make_tile3_tmap(&mq, Q, qc, S, nq, S * qc, kTile);
@@ -768,6 +770,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.S = s.S;
     p.causal = s.causal;
     p.bshd = s.bshd;
+    p.d_real = s.D;
     p.n_tiles = (s.S + kTile - 1) / kTile;
     p.G = s.G();
     p.scale = s.scale;
@@ -790,7 +793,7 @@ extern "C" int gqa_debug_copy_bwd_trace(long long* host) {
 int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
                           const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV,
                           const Shape& s, unsigned int* status, cudaStream_t stream) {
-    if (s.D == 64)
+    if (s.Dp() == 64)
         return launch_bwd_t<64>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
     return launch_bwd_t<128>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
 }

@@ -70,6 +70,7 @@ struct FwdParams {
     float* LSE;
     unsigned int* status;
     int Hq, Hkv, S, causal, n_pairs, bshd;
+    int d_real;        // head dimension of the tensors (<= D of the kernel; the columns beyond it read as zeros)
     float scale_log2;  // scale * log2(e)
 };
 
@@ -369,7 +370,8 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 const bool row_ok = q0 + t * kTile + r < p.S;
                 const float inv_l = 1.0f / l_run;
                 const size_t grow_ = (size_t)q_row0 + t * kTile + r;
-                __nv_bfloat16* orow = p.bshd ? p.O + ((size_t)(b * p.S + q0 + t * kTile + r) * p.Hq + hq) * D : p.O + grow_ * D;
+                __nv_bfloat16* orow = p.bshd ? p.O + ((size_t)(b * p.S + q0 + t * kTile + r) * p.Hq + hq) * D
+                                             : p.O + grow_ * p.d_real;
 #pragma unroll 1
                 for (int ch = 0; ch < D / 32; ++ch) {
                     uint32_t v[32];
@@ -382,7 +384,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                         o.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * inv_l, __uint_as_float(v[8 * i + 3]) * inv_l);
                         o.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * inv_l, __uint_as_float(v[8 * i + 5]) * inv_l);
                         o.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * inv_l, __uint_as_float(v[8 * i + 7]) * inv_l);
-                        if (row_ok) *reinterpret_cast<uint4*>(orow + ch * 32 + i * 8) = o;
+                        if (row_ok && ch * 32 + i * 8 < p.d_real) *reinterpret_cast<uint4*>(orow + ch * 32 + i * 8) = o;
                     }
                 }
                 if (p.LSE && row_ok) p.LSE[grow_] = (m_run * c + log2f(l_run)) * kLn2;
@@ -405,7 +407,8 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
     using Cfg = FwdCfg<D>;
     CUtensorMap mq, mk, mv;
     // see the coordinates in the kernel
-    const uint64_t S = s.S, qc = s.bshd ? (uint64_t)s.Hq * D : D, kc = s.bshd ? (uint64_t)s.Hkv * D : D;
+    // (the matrices are s.D columns wide; a box that reaches beyond them reads zeros there)
+    const uint64_t S = s.S, qc = s.bshd ? (uint64_t)s.Hq * D : s.D, kc = s.bshd ? (uint64_t)s.Hkv * D : s.D;
     const uint64_t nq = s.bshd ? s.B : (uint64_t)s.B * s.Hq, nkv = s.bshd ? s.B : (uint64_t)s.B * s.Hkv;
     int rc = make_tile3_tmap(&mq, Q, qc, S, nq, S * qc, kTile);
     if (rc) return rc;
@@ -424,6 +427,7 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
     p.S = s.S;
     p.causal = s.causal;
     p.bshd = s.bshd;
+    p.d_real = s.D;
     p.n_pairs = (s.S + 2 * kTile - 1) / (2 * kTile);
     p.scale_log2 = s.scale * kLog2e;
     dim3 grid(p.n_pairs, s.Hq, s.B);
@@ -443,7 +447,7 @@ extern "C" int gqa_debug_copy_fwd_trace(long long* host) {
 
 int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,
                      unsigned int* status, cudaStream_t stream) {
-    if (s.D == 64) return launch_fwd_t<64>(Q, K, V, O, LSE, s, status, stream);
+    if (s.Dp() == 64) return launch_fwd_t<64>(Q, K, V, O, LSE, s, status, stream);
     return launch_fwd_t<128>(Q, K, V, O, LSE, s, status, stream);
 }
 

@@ -177,7 +177,7 @@ extern "C" const char* gqa_status_string(int status) {
     switch (status) {
         case GQA_OK: return "ok";
         case GQA_ERR_BAD_ARGUMENT: return "bad argument (null, non-positive or misaligned)";
-        case GQA_ERR_UNSUPPORTED: return "unsupported shape (need D in {64,128}, Hq % Hkv == 0, B*Hq*S < 2^31)";
+        case GQA_ERR_UNSUPPORTED: return "unsupported shape (need D a multiple of 8 up to 128 (64 or 128 with GQA_LAYOUT_BSHD), Hq % Hkv == 0, B*Hq*S < 2^31)";
         case GQA_ERR_WORKSPACE: return "workspace missing or too small";
         case GQA_ERR_CUDA: return "CUDA call failed";
         case GQA_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";

@@ -13,6 +13,10 @@ struct Shape {
     // LSE and the workspace arrays are always in [B,Hq,S] row order.
     int bshd = 0;
     int G() const { return Hq / Hkv; }
+    // Head dimensions other than 64 and 128 run on the kernel of the next size up: the tensor maps describe the real
+    // D columns, the 64-column boxes read zeros beyond them (out-of-bounds fill), zero columns add nothing to any
+    // product, and the epilogues store only the real columns.
+    int Dp() const { return D <= 64 ? 64 : 128; }
     size_t q_rows() const { return (size_t)B * Hq * S; }
     size_t kv_rows() const { return (size_t)B * Hkv * S; }
 };
@@ -32,7 +36,7 @@ struct BwdWorkspace {
         dq_turn_off = delta_cols_off + up(s.q_rows() * 16);
         dq_turn_bytes = (size_t)s.B * s.Hq * ((s.S + 127) / 128) * 4 * sizeof(unsigned int);  // per tile and drain warp
         dq_accum_off = dq_turn_off + up(dq_turn_bytes);
-        total = dq_accum_off + up(s.q_rows() * (size_t)s.D * sizeof(float));
+        total = dq_accum_off + up(s.q_rows() * (size_t)s.Dp() * sizeof(float));  // accumulator rows are Dp wide
     }
 };
 
@@ -44,8 +48,9 @@ int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float
                           void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream,
                           int S_bshd = 0, int H_bshd = 0);
 // Stage 3 of the backward: dQ = bf16(scale * dq_accum) (dQ in [B,S,H,D] order when S_bshd / H_bshd are given).
-int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream,
-                       int D = 0, int S_bshd = 0, int H_bshd = 0);
+// `rows` rows of Dp fp32 accumulator columns -> rows of D bf16 columns.
+int launch_dq_finalise(const float* dq_accum, void* dQ, size_t rows, float scale, cudaStream_t stream,
+                       int D, int S_bshd = 0, int H_bshd = 0);
 
 // Tensor-core forward (tcgen05 + TMEM + TMA).
 int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float* LSE, const Shape& s,

@@ -23,13 +23,16 @@ __device__ __forceinline__ uint2 split3_bf16(float x) {
 }
 
 // One group of D/8 lanes per row; each lane owns 8 consecutive elements (one 16-byte load
-// from O and one from dO).  A warp covers 256/D rows per step.
+// from O and one from dO).  A warp covers 256/D rows per step.  D is the padded head dimension (64 or 128, the
+// width of an accumulator row); O and dO rows hold `d_real` <= D columns.
 template <int D>
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO, const float* __restrict__ lse,
                       float inv_scale, float* __restrict__ delta, uint4* __restrict__ lse_cols,
-                      uint4* __restrict__ delta_cols, float4* __restrict__ dq_accum, size_t rows, int S_bshd, int H_bshd) {
+                      uint4* __restrict__ delta_cols, float4* __restrict__ dq_accum, size_t rows, int S_bshd, int H_bshd,
+                      int d_real) {
     constexpr int kLanesPerRow = D / 8;
+    const int real8 = d_real / 8;  // 16-byte groups per O / dO row
     constexpr int kRowsPerWarp = 32 / kLanesPerRow;
     const int lane = threadIdx.x & 31;
     const size_t warp_global = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -45,8 +48,9 @@ bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO,
                 const size_t s_ = row % S_bshd, bh = row / S_bshd;
                 src = ((bh / H_bshd) * S_bshd + s_) * H_bshd + bh % H_bshd;
             }
-            const uint4 a = O[src * kLanesPerRow + part];
-            const uint4 b = dO[src * kLanesPerRow + part];
+            const bool in_row = part < real8;
+            const uint4 a = in_row ? O[src * real8 + part] : make_uint4(0u, 0u, 0u, 0u);
+            const uint4 b = in_row ? dO[src * real8 + part] : make_uint4(0u, 0u, 0u, 0u);
             const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -72,13 +76,14 @@ bwd_preprocess_kernel(const uint4* __restrict__ O, const uint4* __restrict__ dO,
     }
 }
 
-// n8 groups of eight elements; per8 = D / 8 groups per row.  The accumulator is in [B,H,S] row order, dQ may be
-// stored [B,S,H,D] (S_bshd, H_bshd non-zero).
+// n8 groups of eight output elements; per8 = D / 8 groups per dQ row, acc8 = groups per accumulator row (the padded
+// head dimension / 8).  The accumulator is in [B,H,S] row order, dQ may be stored [B,S,H,D] (S_bshd, H_bshd non-zero).
 __global__ void __launch_bounds__(256)
-dq_finalise_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, size_t n8, float scale, int per8, int S_bshd,
-                   int H_bshd) {
+dq_finalise_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, size_t n8, float scale, int per8, int acc8,
+                   int S_bshd, int H_bshd) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
-        const float4 a = acc[2 * i], b = acc[2 * i + 1];
+        const size_t src = (i / per8) * acc8 + i % per8;
+        const float4 a = acc[2 * src], b = acc[2 * src + 1];
         __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * scale, a.y * scale);
         __nv_bfloat162 p1 = __floats2bfloat162_rn(a.z * scale, a.w * scale);
         __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x * scale, b.y * scale);
@@ -113,29 +118,30 @@ int grid_for(size_t work_items, int per_block) {
 int launch_bwd_preprocess(const void* O, const void* dO, const float* lse, float inv_scale, float* delta,
                           void* lse_cols, void* delta_cols, float* dq_accum, size_t rows, int D, cudaStream_t stream,
                           int S_bshd, int H_bshd) {
-    const int rows_per_block = (256 / 32) * (256 / D);
+    const int Dp = D <= 64 ? 64 : 128;
+    const int rows_per_block = (256 / 32) * (256 / Dp);
     const int grid = grid_for(rows, rows_per_block);
-    if (D == 64)
+    if (Dp == 64)
         bwd_preprocess_kernel<64><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
                                                             lse, inv_scale, delta, static_cast<uint4*>(lse_cols),
                                                             static_cast<uint4*>(delta_cols),
-                                                            reinterpret_cast<float4*>(dq_accum), rows, S_bshd, H_bshd);
+                                                            reinterpret_cast<float4*>(dq_accum), rows, S_bshd, H_bshd, D);
     else
         bwd_preprocess_kernel<128><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(O), static_cast<const uint4*>(dO),
                                                              lse, inv_scale, delta, static_cast<uint4*>(lse_cols),
                                                             static_cast<uint4*>(delta_cols),
-                                                            reinterpret_cast<float4*>(dq_accum), rows, S_bshd, H_bshd);
+                                                            reinterpret_cast<float4*>(dq_accum), rows, S_bshd, H_bshd, D);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;
 }
 
-int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scale, cudaStream_t stream, int D,
+int launch_dq_finalise(const float* dq_accum, void* dQ, size_t rows, float scale, cudaStream_t stream, int D,
                        int S_bshd, int H_bshd) {
-    const size_t n8 = elems / 8;
+    const size_t n8 = rows * (size_t)(D / 8);
     const int grid = grid_for(n8, 256);
     dq_finalise_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(dq_accum), static_cast<uint4*>(dQ), n8,
-                                                 scale, D > 0 ? D / 8 : 1, D > 0 ? S_bshd : 0, H_bshd);
+                                                 scale, D / 8, (D <= 64 ? 64 : 128) / 8, S_bshd, H_bshd);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;
@@ -145,7 +151,7 @@ int launch_dq_finalise(const float* dq_accum, void* dQ, size_t elems, float scal
 
 extern "C" int gqa_bwd_delta(const void* O, const void* dO, float* delta, size_t rows, int D, gqa_stream_t stream) {
     if (!O || !dO || !delta || rows == 0) return GQA_ERR_BAD_ARGUMENT;
-    if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
+    if (D < 8 || D > 128 || D % 8 != 0) return GQA_ERR_UNSUPPORTED;
     if (!gqa::aligned16(O) || !gqa::aligned16(dO)) return GQA_ERR_BAD_ARGUMENT;
     return gqa::launch_bwd_preprocess(O, dO, nullptr, 0.f, delta, nullptr, nullptr, nullptr, rows, D,
                                       reinterpret_cast<cudaStream_t>(stream));

@@ -7,7 +7,10 @@
  *   K, V, dK, dV : [B, Hkv, S, D]  bf16, contiguous, row-major
  *   LSE          : [B, Hq, S]      fp32, natural log of sum_j exp(scale * q_i . k_j)
  *   query head hq reads KV head hq / (Hq / Hkv)
- * Supported: D in {64, 128}, any S >= 1 (the reference needs S % 64 == 0 in the backward,
+ * Supported: D a multiple of 8 up to 128 (the reference's tensor-core kernels fix D = 128, its first two
+ * generations take D % 16 == 0, src/attention/GQA_bwd.cu:391-393; here D = 64 and D = 128 are the native sizes and
+ * the others run on the next one up, reading the missing columns as zeros), any S >= 1 (the reference needs
+ * S % 64 == 0 in the backward,
  * src/attention/GQA_bwd_baseline.cu:549-602, and S % 256 == 0 in the forward,
  * src/attention/GQA_fwd_ref.cu:352; here a partial last tile is masked), Hq a multiple of Hkv,
  * all pointers 16-byte aligned, scale finite and > 0.  Anything else returns an error code; the
@@ -31,7 +34,7 @@ typedef struct CUstream_st* gqa_stream_t; /* same handle as cudaStream_t */
 typedef enum gqa_status {
     GQA_OK = 0,
     GQA_ERR_BAD_ARGUMENT = -1,   /* null pointer, non-positive size, misaligned pointer, scale not finite or <= 0 */
-    GQA_ERR_UNSUPPORTED = -2,    /* shape outside the supported set (D in {64,128}, Hq % Hkv == 0) */
+    GQA_ERR_UNSUPPORTED = -2,    /* shape outside the supported set (D % 8 == 0, D <= 128, Hq % Hkv == 0) */
     GQA_ERR_WORKSPACE = -3,      /* workspace missing or smaller than gqa_bwd_workspace_bytes() */
     GQA_ERR_CUDA = -4,           /* a CUDA runtime/driver call failed (see gqa_last_cuda_error) */
     GQA_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up; outputs are invalid */
@@ -61,7 +64,8 @@ int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE,
  * GQA_LAYOUT_BSHD: Q and O are [B,S,Hq,D] and K and V [B,S,Hkv,D] (sequence-major, the layout the reference's
  * harness hands to the FlashAttention and FlashInfer adapters, harness/competitors.py:116-122) instead of the
  * canonical [B,H,S,D]; the tiles are fetched through tensor maps over the B matrices [S, H*D], so no transposed
- * copy is made.  LSE stays [B,Hq,S].  Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
+ * copy is made.  LSE stays [B,Hq,S].  This layout needs D = 64 or D = 128 (a head's columns are followed by the
+ * next head's, so nothing reads as zero padding).  Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
  */
 #define GQA_LAYOUT_BSHD 2u
 int gqa_fwd_ex(const void* Q, const void* K, const void* V, void* O, float* LSE,

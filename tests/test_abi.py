@@ -45,7 +45,11 @@ def test_workspace_bytes_formula(gqa_lib):
     assert need >= rows * D * 4 + 2 * rows * 4 + 256
     assert need % 256 == 0
     # unsupported shapes report zero
-    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 96, 0) == 0
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 100, 0) == 0        # rows must be multiples of 16 bytes
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 136, 0) == 0
+    # other head dimensions run on the next native size up: the accumulator rows are padded to it
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 96, 0) == gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 128, 0)
+    assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 40, 0) == need
     assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S + 60, D, 0) > need   # any S: partial tiles are masked
     assert gqa_lib.gqa_bwd_workspace_bytes(B, 10, 4, S, D, 0) == 0
 
@@ -54,7 +58,9 @@ def test_argument_validation_needs_no_device(gqa_lib, selftest_lib):
     p = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
     assert gqa_lib.gqa_fwd(None, p, p, p, None, 1, 4, 2, 128, 64, 0, 0.125, None) == -1
     assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 0, 64, 0, 0.125, None) == -1        # S <= 0
-    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 128, 80, 0, 0.125, None) == -2      # D
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 128, 100, 0, 0.125, None) == -2     # D % 8
+    assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 4, 2, 128, 136, 0, 0.125, None) == -2     # D > 128
+    assert gqa_lib.gqa_fwd_ex(p, p, p, p, None, 1, 4, 2, 128, 96, 0, 0.125, None, 2) == -2  # [B,S,H,D] needs D = 64 / 128
     assert gqa_lib.gqa_fwd(p, p, p, p, None, 1, 5, 2, 128, 64, 0, 0.125, None) == -2      # Hq % Hkv
     assert gqa_lib.gqa_fwd(p, p, p, p, None, 0, 4, 2, 128, 64, 0, 0.125, None) == -1      # B <= 0
     mis = ctypes.c_void_p(4096 + 2)
@@ -69,7 +75,7 @@ def test_argument_validation_needs_no_device(gqa_lib, selftest_lib):
     assert selftest_lib.gqa_selftest_umma_cycles(p, p, p, 128, 0, 1 << 20, 0, None, None) == -1  # reps capped
     assert selftest_lib.gqa_selftest_timeout(p, 10 ** 10, 1, None) == -1                           # limit capped
     assert selftest_lib.gqa_selftest_timeout(None, 1000, 1, None) == -1
-    assert gqa_lib.gqa_bwd_delta(p, p, p, 16, 32, None) == -2
+    assert gqa_lib.gqa_bwd_delta(p, p, p, 16, 36, None) == -2
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

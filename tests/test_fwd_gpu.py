@@ -90,7 +90,7 @@ def test_forward_headline_shape_properties(gqa_lib):
 
 
 def test_forward_rejects_unsupported_shapes(gqa_lib):
-    q = torch.zeros(1, 2, 192, 96, dtype=torch.bfloat16, device="cuda")   # head dim other than 64 / 128
+    q = torch.zeros(1, 2, 192, 100, dtype=torch.bfloat16, device="cuda")  # head dim not a multiple of 8
     with pytest.raises(capi.GqaError) as e:
         ops.gqa_forward(q, q, q)
     assert e.value.status == -2
