@@ -48,9 +48,9 @@ LONG_CONTEXT = dict(B=1, Hq=64, Hkv=8, S=32768, D=128, causal=True)
 METRIC = "GQA bwd TFLOP/s (B8 Hq12 Hkv4 S4096 D64 bf16)"
 NOMINAL_BF16_TFLOPS = 2250.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the backward main kernel from one ncu capture at B=4
-# (B4 Hq12 Hkv4 S4096 D64: 123.8 MB read + 30.3 MB written = 154 MB), scaled by 2 to the headline batch: the
+# (B4 Hq12 Hkv4 S4096 D64: 124.0 MB read + 26.9 MB written = 150.9 MB), scaled by 2 to the headline batch: the
 # (batch, KV-head) groups are independent, so traffic grows in proportion to B.
-MAIN_KERNEL_DRAM_BYTES_PER_LAUNCH = 2 * 154.2e6
+MAIN_KERNEL_DRAM_BYTES_PER_LAUNCH = 2 * 150.9e6
 # dram bytes of the forward kernel at B4 Hq12 Hkv4 S4096 D64 (42.0 MB read + 0.8 MB written), same scaling
 FWD_KERNEL_DRAM_BYTES_PER_LAUNCH = 2 * 42.8e6
 
@@ -299,10 +299,11 @@ def sharded_problem(name, shape, tensors, gqa, ops, sharding, timer, dist, rank,
     if n > 0:
         sq, sk, sv, sdo = parts
         so, slse = gqa.gqa_forward(sq, sk, sv, causal=causal, scale=sc)
-        ws = torch.empty(gqa.bwd_workspace_bytes(n, G, 1, S, D, causal), dtype=torch.uint8, device=dev)
+        # a shard may hold too few KV tiles to fill the GPU evenly: let the library split tiles by query head
+        ws = torch.empty(gqa.bwd_workspace_bytes(n, G, 1, S, D, causal, split_heads=True), dtype=torch.uint8, device=dev)
         sdq, sdk, sdv = torch.empty_like(sq), torch.empty_like(sk), torch.empty_like(sv)
         my_ms = timer(lambda: gqa.gqa_backward(sq, sk, sv, so, sdo, slse, causal=causal, scale=sc, workspace=ws,
-                                               dq=sdq, dk=sdk, dv=sdv), reps=5, warmup=2)
+                                               dq=sdq, dk=sdk, dv=sdv, split_heads=True), reps=5, warmup=2)
         ops.check_status(ws)
         del ws
     else:
@@ -331,8 +332,11 @@ def sharded_problem(name, shape, tensors, gqa, ops, sharding, timer, dist, rank,
             one_ms = my_ms
         ops.check_status(ws)
         gdq, gdk, gdv = (g.reshape(t.shape) for g, t in zip(gathered, (dq, dk, dv)))
-        dq_m = tensor_metrics(gdq, dq)
-        gather_ok = bool(torch.equal(gdk, dk) and torch.equal(gdv, dv) and dq_m["rel_rms"] <= 2e-3)
+        dq_m, dk_m, dv_m = tensor_metrics(gdq, dq), tensor_metrics(gdk, dk), tensor_metrics(gdv, dv)
+        bit_equal = bool(torch.equal(gdk, dk) and torch.equal(gdv, dv))
+        # dK/dV are bit-equal to the unsharded run unless a shard used the head split (fp32 partial sums added in a
+        # fixed order: same values up to the last bf16 bit)
+        gather_ok = bool(dq_m["rel_rms"] <= 2e-3 and (bit_equal or max(dk_m["rel_rms"], dv_m["rel_rms"]) <= 2e-3))
         slow = max(all_ms)
         flops = bwd_flops(B, Hq, S, D, causal)
         result = {
@@ -347,8 +351,11 @@ def sharded_problem(name, shape, tensors, gqa, ops, sharding, timer, dist, rank,
                                                                      (sharding.group_range(r, world, n_groups)
                                                                       for r in range(world)))),
             "gather": "NCCL all_gather of dQ/dK/dV shards" if dist is not None else "single rank (no gather)",
-            "gather_ok": gather_ok, "dk_dv_bit_equal_to_unsharded": bool(torch.equal(gdk, dk) and torch.equal(gdv, dv)),
+            "gather_ok": gather_ok, "dk_dv_bit_equal_to_unsharded": bit_equal,
+            "dk_dv_rel_rms_vs_unsharded": max(dk_m["rel_rms"], dv_m["rel_rms"]),
             "dq_rel_rms_vs_unsharded": dq_m["rel_rms"],
+            "head_split": "GQA_BWD_SPLIT_HEADS passed for the shards (the library splits only when a shard has too few "
+                          "KV tiles to fill its GPU)",
         }
         if sdpa_sample is not None:  # fp32 SDPA autograd of the first batches (the CPU-baseline sample)
             _, rdq, rdk, rdv = sdpa_sample

@@ -16,6 +16,7 @@ _SELFTEST_LIB = None
 GQA_OK = 0
 GQA_BWD_DETERMINISTIC = 1
 GQA_LAYOUT_BSHD = 2
+GQA_BWD_SPLIT_HEADS = 4
 STATUS_NAMES = {
     0: "GQA_OK", -1: "GQA_ERR_BAD_ARGUMENT", -2: "GQA_ERR_UNSUPPORTED", -3: "GQA_ERR_WORKSPACE",
     -4: "GQA_ERR_CUDA", -5: "GQA_ERR_DEVICE_TIMEOUT", -6: "GQA_ERR_ARCH",
@@ -29,6 +30,7 @@ EXPORTS = {
     "gqa_fwd_ex": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp, ctypes.c_uint]),
     "launch_gqa": (_i, [_vp, _vp, _vp, _vp, _fp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
+    "gqa_bwd_workspace_bytes_ex": (_sz, [_i, _i, _i, _i, _i, _i, ctypes.c_uint]),
     "gqa_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "gqa_bwd_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp,
                         ctypes.c_uint]),

@@ -79,8 +79,17 @@ extern "C" int launch_gqa(const void* Q, const void* K, const void* V, void* O, 
 extern "C" size_t gqa_bwd_workspace_bytes(int B, int Hq, int Hkv, int S, int D, int causal) {
     (void)causal;
     if (check_shape(B, Hq, Hkv, S, D) != GQA_OK) return 0;
+    (void)causal;
     const Shape s{B, Hq, Hkv, S, D, 0, 0.f};
     return gqa::BwdWorkspace(s).total;
+}
+
+extern "C" size_t gqa_bwd_workspace_bytes_ex(int B, int Hq, int Hkv, int S, int D, int causal, unsigned int flags) {
+    if (check_shape(B, Hq, Hkv, S, D) != GQA_OK) return 0;
+    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD | GQA_BWD_SPLIT_HEADS)) return 0;
+    Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, 0.f};
+    s.bshd = (flags & GQA_LAYOUT_BSHD) ? 1 : 0;
+    return gqa::BwdWorkspace(s, (flags & GQA_BWD_SPLIT_HEADS) ? gqa::bwd_head_parts(s) : 1).total;
 }
 
 namespace {
@@ -89,7 +98,7 @@ namespace {
 int run_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE, void* dQ,
             void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale, void* workspace,
             size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev, unsigned int flags = 0) {
-    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD)) return GQA_ERR_BAD_ARGUMENT;
+    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD | GQA_BWD_SPLIT_HEADS)) return GQA_ERR_BAD_ARGUMENT;
     if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
@@ -99,7 +108,8 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
         if (!gqa::aligned16(p)) return GQA_ERR_BAD_ARGUMENT;
     Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
     s.bshd = (flags & GQA_LAYOUT_BSHD) ? 1 : 0;
-    const gqa::BwdWorkspace ws(s);
+    const int parts = (flags & GQA_BWD_SPLIT_HEADS) ? gqa::bwd_head_parts(s) : 1;
+    const gqa::BwdWorkspace ws(s, parts);
     if (!workspace || workspace_bytes < ws.total) {
         gqa::note_text("backward workspace: need %zu bytes, got %zu", ws.total, workspace ? workspace_bytes : (size_t)0);
         return GQA_ERR_WORKSPACE;
@@ -124,9 +134,15 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
                                     stream, s.bshd ? S : 0, s.bshd ? Hq : 0);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[1], stream));
-    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
+    float* partial = parts > 1 ? reinterpret_cast<float*>(w + ws.partial_off) : nullptr;
+    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, parts,
+                                    partial, stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[2], stream));
+    if (parts > 1) {
+        rc = gqa::launch_dkdv_reduce(partial, dK, dV, s, parts, stream);
+        if (rc) return rc;
+    }
     rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows(), scale, stream, D, s.bshd ? S : 0, s.bshd ? Hq : 0);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[3], stream));

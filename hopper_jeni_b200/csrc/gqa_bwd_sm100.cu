@@ -50,6 +50,11 @@ using namespace sm100;
 #define GQA_BWD_TRACE_BLOCK 0
 #endif
 __device__ long long g_bwd_trace[5][64][4];
+__device__ long long g_bwd_marks[16];
+#define GQA_MARK(slot)                                                                            \
+    do {                                                                                           \
+        if (blockIdx.x == GQA_BWD_TRACE_BLOCK && (threadIdx.x & 31) == 0) g_bwd_marks[slot] = clock64(); \
+    } while (0)
 #define GQA_TRACE(role, it, slot)                                                                  \
     do {                                                                                           \
         if (blockIdx.x == GQA_BWD_TRACE_BLOCK && (it) < 64 && (threadIdx.x & 31) == 0) g_bwd_trace[role][it][slot] = clock64(); \
@@ -57,6 +62,9 @@ __device__ long long g_bwd_trace[5][64][4];
 #else
 #define GQA_TRACE(role, it, slot) \
     do {                          \
+    } while (0)
+#define GQA_MARK(slot) \
+    do {               \
     } while (0)
 #endif
 
@@ -128,6 +136,12 @@ struct BwdParams {
     __nv_bfloat16* dV;
     unsigned int* status;
     unsigned int* dq_turn;  // deterministic mode: one counter per 32 query rows (zeroed), else nullptr
+    // Head split: with `parts` > 1 a KV tile's work is cut over `parts` thread blocks, each looping over G / parts
+    // of the group's query heads and storing its dK / dV sums as fp32 into `partial` ([part][dV, dK][key row][D of
+    // the kernel]); a fixed-order sum over the parts then rounds once (dkdv_reduce_kernel).  Used when there are too
+    // few KV tiles to fill the SMs evenly (a long-context problem sharded down to one KV head per GPU).
+    float* partial;
+    int parts;
     int Hq, Hkv, S, causal, n_tiles, G, bshd;
     int d_real;  // head dimension of the tensors (<= D of the kernel; the columns beyond it read as zeros)
     float scale, scale_log2;
@@ -154,6 +168,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (threadIdx.x == 0) atomicCAS(p.status, 0u, 0x80000000u | (99u << 20));
         return;
     }
+    if (threadIdx.x == 0) GQA_MARK(0);
     uint8_t* sK = smem + Cfg::kOffK;
     uint8_t* sV = smem + Cfg::kOffV;
     uint8_t* sQ = smem + Cfg::kOffQ;
@@ -194,23 +209,25 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // so the CTAs that run at the same time share their Q/dO tiles and dQ accumulator rows in L2 (measured
     // +6.7 % at the headline shape).  Causal: the KV tile is the slow index so the longest items start first
     // (load balance matters more there: measured +6 %). ----
-    const int groups = gridDim.x / p.n_tiles;  // B * Hkv
+    const int groups = gridDim.x / (p.n_tiles * p.parts);  // B * Hkv
+    const int part = (int)blockIdx.x % p.parts, item = (int)blockIdx.x / p.parts;  // the parts of a tile are neighbours
     // The deterministic mode also takes the KV tile as the slow index: the CTAs of one group that run at the same
     // time must reduce one after the other, and this order keeps only a few of them in flight together.
     const bool kt_major = p.causal || p.dq_turn != nullptr;
-    const int kt = kt_major ? (int)blockIdx.x / groups : (int)blockIdx.x % p.n_tiles;
-    const int grp = kt_major ? (int)blockIdx.x % groups : (int)blockIdx.x / p.n_tiles;
+    const int kt = kt_major ? item / groups : item % p.n_tiles;
+    const int grp = kt_major ? item % groups : item / p.n_tiles;
     const int b = grp / p.Hkv, hkv = grp % p.Hkv;
     const int qt0 = p.causal ? kt : 0;
     const int n_qt = p.n_tiles - qt0;
-    const int n_iter = p.G * n_qt;
+    const int g_local = p.G / p.parts;  // query heads this thread block loops over
+    const int n_iter = g_local * n_qt;
     // Tensor-map coordinates (x = column, y = position in the sequence, z = matrix).  [B,H,S,D] is B*H matrices
     // [S, D]; [B,S,H,D] is B matrices [S, H*D] with the head at x = head * D.  The workspace arrays are B*Hq
     // matrices [S, .].  Rows at y >= S read as zeros and are skipped by the reductions, so S may be any length:
     // keys beyond S give zero rows of K and V (their dK / dV rows are not stored and their dS meets a zero row of
     // K in dQ), queries beyond S give zero rows of Q, dO and of the -LSE / -Delta columns (P = 1, dS = 0).
     const int kv_x = p.bshd ? hkv * D : 0, kv_z = p.bshd ? b : b * p.Hkv + hkv;
-    auto head_of = [&](int it) { return hkv * p.G + it / n_qt; };        // query head inside the batch
+    auto head_of = [&](int it) { return hkv * p.G + part * g_local + it / n_qt; };  // query head inside the batch
     auto q_y_of = [&](int it) { return (qt0 + it % n_qt) * kTile; };     // first query position of the tile
     auto q_x_of = [&](int it) { return p.bshd ? head_of(it) * D : 0; };
     auto q_z_of = [&](int it) { return p.bshd ? b : b * p.Hq + head_of(it); };
@@ -255,6 +272,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (warp == Cfg::kWarpMmaS) tmem_dealloc(tmem, Cfg::kTmemCols);
         return;
     }
+    if (threadIdx.x == 0) GQA_MARK(1);
     const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ);
     const uint32_t do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
 
@@ -535,8 +553,10 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             if (!turn_mine) break;  // a bounded wait gave up: the abort flag is set
             GQA_TRACE(2, it, 1);
         }
+        if (warp == 0) GQA_MARK(7);
         release_held();
         if (lane == 0) bulk_wait_all();
+        if (warp == 0) GQA_MARK(8);
     } else if (warp < Cfg::kWarpTma) {
         // ======================= elementwise warpgroups (P^T and dS^T) =======================
         // Rotated by half an iteration: the body of iteration `it` turns dP^T(it) into dS^T(it) and then
@@ -620,6 +640,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 
         // ---- prologue: P^T(0)
         ok = mbar_wait(&s_full[0], 0, ctx, 51);
+        if (trace_me) GQA_MARK(2);
         if (ok) {
             tc_fence_after_sync();
             const bool masked0 = p.causal != 0;  // iteration 0 is the diagonal tile when causal
@@ -686,7 +707,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             if (trace_me) GQA_TRACE(0, it, 3);
         }
         // ---- epilogue: dV and scale*dK of this key row, a quarter of the columns per warpgroup ----
+        if (trace_me) GQA_MARK(4);
         if (ok) ok = mbar_wait(acc_full, 0, ctx, 55);
+        if (trace_me) GQA_MARK(5);
         if (ok) {
             tc_fence_after_sync();
             // key rows beyond the end of the sequence are not stored (the TMEM loads below are warp-wide
@@ -701,12 +724,25 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             for (int which = 0; which < 2; ++which) {
                 const uint32_t tA = tmem + lane_addr + (which == 0 ? Cfg::kColDV : Cfg::kColDK) + w * kQuarter;
                 __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + kv_elem + w * kQuarter;
+                // head split: fp32 sums of this part, [part][which][key row in [B,Hkv,S] order][D]
+                float* pdst = p.parts > 1 ? p.partial + (((size_t)(part * 2 + which) * ((size_t)groups * p.S)) +
+                                                         (size_t)grp * p.S + kv_pos) * D + w * kQuarter
+                                          : nullptr;
                 const float mul = which == 0 ? 1.0f : p.scale;
 #pragma unroll
                 for (int ch = 0; ch < kQuarter / 16; ++ch) {
                     uint32_t v[16];
                     tmem_ld16(tA + ch * 16, v);
                     tmem_wait_ld();
+                    if (p.parts > 1) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (row_ok)
+                                *reinterpret_cast<float4*>(pdst + ch * 16 + i * 4) =
+                                    make_float4(__uint_as_float(v[4 * i + 0]) * mul, __uint_as_float(v[4 * i + 1]) * mul,
+                                                __uint_as_float(v[4 * i + 2]) * mul, __uint_as_float(v[4 * i + 3]) * mul);
+                        continue;
+                    }
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         uint4 o;
@@ -722,8 +758,10 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     }
 
     // ---- teardown ---------------------------------------------------------------
+    if (warp == kWarpEw0) GQA_MARK(6);
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) GQA_MARK(9);
     if (warp == Cfg::kWarpMmaS) {
         if (*abort_flag != 0) abort_grace_period();  // in-flight copies and MMAs land before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
@@ -733,7 +771,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 template <int D>
 int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
                  const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV, const Shape& s,
-                 unsigned int* status, cudaStream_t stream) {
+                 unsigned int* status, int parts, float* partial, cudaStream_t stream) {
     using Cfg = BwdCfg<D>;
     CUtensorMap mq, mk, mv, mdo;
     // see the coordinates in the kernel
@@ -765,6 +803,8 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.dV = static_cast<__nv_bfloat16*>(dV);
     p.status = status;
     p.dq_turn = dq_turn;
+    p.partial = partial;
+    p.parts = parts;
     p.Hq = s.Hq;
     p.Hkv = s.Hkv;
     p.S = s.S;
@@ -775,7 +815,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.G = s.G();
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
-    const unsigned grid = (unsigned)(p.n_tiles * s.B * s.Hkv);
+    const unsigned grid = (unsigned)(p.n_tiles * s.B * s.Hkv * parts);
     gqa_bwd_sm100_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, mlse, mdlt, p);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
@@ -788,14 +828,20 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
 extern "C" int gqa_debug_copy_bwd_trace(long long* host) {
     return (int)cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(g_bwd_trace));
 }
+extern "C" int gqa_debug_copy_bwd_marks(long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, g_bwd_marks, sizeof(g_bwd_marks));
+}
 #endif
 
 int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
                           const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV,
-                          const Shape& s, unsigned int* status, cudaStream_t stream) {
+                          const Shape& s, unsigned int* status, int parts, float* partial, cudaStream_t stream) {
+    if (parts < 1 || s.G() % parts != 0 || (parts > 1 && !partial)) return GQA_ERR_BAD_ARGUMENT;
     if (s.Dp() == 64)
-        return launch_bwd_t<64>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
-    return launch_bwd_t<128>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, stream);
+        return launch_bwd_t<64>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, parts, partial,
+                                stream);
+    return launch_bwd_t<128>(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, parts, partial,
+                             stream);
 }
 
 }  // namespace gqa

@@ -102,6 +102,31 @@ dq_finalise_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, size_
     }
 }
 
+// out = bf16(sum over the parts, in part order, of the fp32 partial sums); n8 groups of eight output elements,
+// per8 = D / 8 groups per output row, acc8 = groups per partial row, part_stride8 = groups between two parts' copies of
+// one tensor.
+__global__ void __launch_bounds__(256)
+dkdv_reduce_kernel(const float4* __restrict__ partial, uint4* __restrict__ out, size_t n8, int per8, int acc8, int parts,
+                   size_t part_stride8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t src = (i / per8) * acc8 + i % per8;
+        float4 a = partial[2 * src], b = partial[2 * src + 1];
+        for (int p = 1; p < parts; ++p) {
+            const float4 c = partial[2 * (src + p * part_stride8)], d = partial[2 * (src + p * part_stride8) + 1];
+            a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+            b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+        }
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+        uint4 o;
+        o.x = *reinterpret_cast<uint32_t*>(&p0);
+        o.y = *reinterpret_cast<uint32_t*>(&p1);
+        o.z = *reinterpret_cast<uint32_t*>(&p2);
+        o.w = *reinterpret_cast<uint32_t*>(&p3);
+        out[i] = o;
+    }
+}
+
 int grid_for(size_t work_items, int per_block) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -145,6 +170,58 @@ int launch_dq_finalise(const float* dq_accum, void* dQ, size_t rows, float scale
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;
+}
+
+int launch_dkdv_reduce(const float* partial, void* dK, void* dV, const Shape& s, int parts, cudaStream_t stream) {
+    const size_t rows = s.kv_rows(), n8 = rows * (size_t)(s.D / 8);
+    const int acc8 = s.Dp() / 8;
+    const size_t tensor_stride8 = rows * acc8;  // [part][dV, dK][rows][Dp]: the two tensors of a part are neighbours
+    const int grid = grid_for(n8, 256);
+    for (int which = 0; which < 2; ++which) {
+        dkdv_reduce_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(partial) + 2 * which * tensor_stride8,
+                                                     static_cast<uint4*>(which == 0 ? dV : dK), n8, s.D / 8, acc8, parts,
+                                                     2 * tensor_stride8);
+        count_launch();
+    }
+    GQA_CUDA_TRY(cudaGetLastError());
+    return GQA_OK;
+}
+
+int bwd_head_parts(const Shape& s) {
+    constexpr int kSms = 148;  // the library is sm_100a-only: B200
+    const int G = s.G(), n_tiles = (s.S + 127) / 128;
+    const long items = (long)n_tiles * s.B * s.Hkv;
+    if (G == 1 || s.bshd || items >= 2 * kSms) return 1;
+    // Estimated makespan (in tile pairs) of list scheduling, longest item first, on the SMs, for every divisor of G;
+    // every item also pays a fixed start/finish cost worth about four tile pairs.  The split is taken only when it
+    // shortens the estimate by more than 8 %: the partial sums and their reduction are not free.
+    auto makespan = [&](int parts) {
+        double load[kSms] = {};
+        const int g_local = G / parts;
+        for (int kt = 0; kt < n_tiles; ++kt) {
+            const double len = (double)g_local * (s.causal ? n_tiles - kt : n_tiles) + 4.0;
+            for (long rep = 0; rep < (long)s.B * s.Hkv * parts; ++rep) {
+                int best = 0;
+                for (int i = 1; i < kSms; ++i)
+                    if (load[i] < load[best]) best = i;
+                load[best] += len;
+            }
+        }
+        double worst = 0;
+        for (double l : load) worst = l > worst ? l : worst;
+        return worst;
+    };
+    int best_parts = 1;
+    double best = makespan(1);
+    for (int parts = 2; parts <= G; ++parts) {
+        if (G % parts) continue;
+        const double m = makespan(parts);
+        if (m < 0.92 * best) {
+            best = m;
+            best_parts = parts;
+        }
+    }
+    return best_parts;
 }
 
 }  // namespace gqa

@@ -80,23 +80,29 @@ def gqa_forward(q, k, v, causal: bool = False, scale: float | None = None, out=N
     return out, lse
 
 
-def bwd_workspace_bytes(B, Hq, Hkv, S, D, causal=False) -> int:
-    return int(capi.load_library().gqa_bwd_workspace_bytes(B, Hq, Hkv, S, D, int(bool(causal))))
+def bwd_workspace_bytes(B, Hq, Hkv, S, D, causal=False, split_heads: bool = False) -> int:
+    """Bytes of scratch ``gqa_backward`` needs; with ``split_heads`` for calls that pass the same option."""
+    lib = capi.load_library()
+    if split_heads:
+        return int(lib.gqa_bwd_workspace_bytes_ex(B, Hq, Hkv, S, D, int(bool(causal)), capi.GQA_BWD_SPLIT_HEADS))
+    return int(lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, D, int(bool(causal))))
 
 
 def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None = None,
                  workspace=None, dq=None, dk=None, dv=None, stream=None, deterministic: bool = False,
-                 layout: str = "bhsd"):
+                 layout: str = "bhsd", split_heads: bool = False):
     """dQ, dK, dV.  Mirrors ``launch_gqa_backward_vj1d`` (G derived from the head counts).
     ``deterministic`` orders the dQ reductions (``GQA_BWD_DETERMINISTIC``): bit-reproducible dQ, slower.
-    ``layout="bshd"``: all bf16 tensors are [B,S,H,D] (``GQA_LAYOUT_BSHD``); LSE is [B,Hq,S] either way."""
+    ``layout="bshd"``: all bf16 tensors are [B,S,H,D] (``GQA_LAYOUT_BSHD``); LSE is [B,Hq,S] either way.
+    ``split_heads`` (``GQA_BWD_SPLIT_HEADS``): let a call with few KV tiles cut each tile's work over several thread
+    blocks by query head (fp32 partial dK/dV, fixed-order sum); the workspace must be sized with the same option."""
     lib = capi.load_library()
     for t, n in ((q, "Q"), (k, "K"), (v, "V"), (o, "O"), (do, "dO")):
         _req(t, n, torch.bfloat16)
     _req(lse, "LSE", torch.float32)
     B, Hq, Hkv, S, D = _dims(q, k, layout)
     scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
-    need = bwd_workspace_bytes(B, Hq, Hkv, S, D, causal)
+    need = bwd_workspace_bytes(B, Hq, Hkv, S, D, causal, split_heads)
     if need == 0:
         capi.check("gqa_bwd_workspace_bytes", -2)
     if workspace is None:
@@ -117,7 +123,8 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
         args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,
                 workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream_ptr(stream))
-        flags = (capi.GQA_BWD_DETERMINISTIC if deterministic else 0) | (capi.GQA_LAYOUT_BSHD if layout == "bshd" else 0)
+        flags = ((capi.GQA_BWD_DETERMINISTIC if deterministic else 0) | (capi.GQA_LAYOUT_BSHD if layout == "bshd" else 0)
+                 | (capi.GQA_BWD_SPLIT_HEADS if split_heads else 0))
         rc = lib.gqa_bwd_ex(*args, flags) if flags else lib.gqa_bwd(*args)
     capi.check("gqa_bwd_ex" if flags else "gqa_bwd", rc)
     return dq, dk, dv

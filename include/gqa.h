@@ -106,8 +106,19 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
  * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.
  * GQA_LAYOUT_BSHD (see gqa_fwd_ex): Q, O, dO, dQ are [B,S,Hq,D] and K, V, dK, dV [B,S,Hkv,D]; LSE stays [B,Hq,S].
  * Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
+ * GQA_BWD_SPLIT_HEADS: for calls with too few KV tiles to fill the GPU evenly (fewer than two per SM: a
+ * long-context problem sharded down to one KV head per GPU, where the longest causal tile alone outlasts the
+ * per-SM average).  The library may then cut every KV tile's work over several thread blocks that each loop over a
+ * part of the group's query heads, store fp32 partial dK / dV sums in the workspace and add them in a fixed order
+ * (the reference's per-head grid + gqa_dkdv_greduce, src/attention/GQA_bwd_baseline.cu:385-403, :594-599, on fp32
+ * partials).  Whether and how far it splits is a function of the shape only (an estimate of the schedule's
+ * makespan); dK and dV stay bit-reproducible from run to run, but their last bits depend on the split, so results
+ * are no longer bit-identical across different shardings of one problem, which is why this is a flag.  The
+ * workspace must come from gqa_bwd_workspace_bytes_ex with the same flags.
  */
 #define GQA_BWD_DETERMINISTIC 1u
+#define GQA_BWD_SPLIT_HEADS 4u
+size_t gqa_bwd_workspace_bytes_ex(int B, int Hq, int Hkv, int S, int D, int causal, unsigned int flags);
 int gqa_bwd_ex(const void* Q, const void* K, const void* V, const void* O, const void* dO,
                const float* LSE, void* dQ, void* dK, void* dV,
                int B, int Hq, int Hkv, int S, int D, int causal, float scale,

@@ -52,6 +52,12 @@ def test_workspace_bytes_formula(gqa_lib):
     assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S, 40, 0) == need
     assert gqa_lib.gqa_bwd_workspace_bytes(B, Hq, Hkv, S + 60, D, 0) > need   # any S: partial tiles are masked
     assert gqa_lib.gqa_bwd_workspace_bytes(B, 10, 4, S, D, 0) == 0
+    # with GQA_BWD_SPLIT_HEADS (4) the query covers the fp32 partial sums of shapes that are split: a shape with
+    # plenty of KV tiles is not, one KV head of a long causal problem is
+    assert gqa_lib.gqa_bwd_workspace_bytes_ex(B, Hq, Hkv, S, D, 0, 4) == need
+    one_head = gqa_lib.gqa_bwd_workspace_bytes(1, 8, 1, 32768, 128, 1)
+    assert gqa_lib.gqa_bwd_workspace_bytes_ex(1, 8, 1, 32768, 128, 1, 4) > one_head
+    assert gqa_lib.gqa_bwd_workspace_bytes_ex(1, 8, 1, 32768, 128, 1, 64) == 0      # unknown flag
 
 
 def test_argument_validation_needs_no_device(gqa_lib, selftest_lib):
