@@ -17,6 +17,7 @@ GQA_OK = 0
 GQA_BWD_DETERMINISTIC = 1
 GQA_LAYOUT_BSHD = 2
 GQA_BWD_SPLIT_HEADS = 4
+GQA_BWD_DQ_SEPARATE = 8
 STATUS_NAMES = {
     0: "GQA_OK", -1: "GQA_ERR_BAD_ARGUMENT", -2: "GQA_ERR_UNSUPPORTED", -3: "GQA_ERR_WORKSPACE",
     -4: "GQA_ERR_CUDA", -5: "GQA_ERR_DEVICE_TIMEOUT", -6: "GQA_ERR_ARCH",

@@ -86,7 +86,7 @@ extern "C" size_t gqa_bwd_workspace_bytes(int B, int Hq, int Hkv, int S, int D, 
 
 extern "C" size_t gqa_bwd_workspace_bytes_ex(int B, int Hq, int Hkv, int S, int D, int causal, unsigned int flags) {
     if (check_shape(B, Hq, Hkv, S, D) != GQA_OK) return 0;
-    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD | GQA_BWD_SPLIT_HEADS)) return 0;
+    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD | GQA_BWD_SPLIT_HEADS | GQA_BWD_DQ_SEPARATE)) return 0;
     Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, 0.f};
     s.bshd = (flags & GQA_LAYOUT_BSHD) ? 1 : 0;
     return gqa::BwdWorkspace(s, (flags & GQA_BWD_SPLIT_HEADS) ? gqa::bwd_head_parts(s) : 1).total;
@@ -98,7 +98,8 @@ namespace {
 int run_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE, void* dQ,
             void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale, void* workspace,
             size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev, unsigned int flags = 0) {
-    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD | GQA_BWD_SPLIT_HEADS)) return GQA_ERR_BAD_ARGUMENT;
+    if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD | GQA_BWD_SPLIT_HEADS | GQA_BWD_DQ_SEPARATE))
+        return GQA_ERR_BAD_ARGUMENT;
     if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
@@ -122,28 +123,37 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
     void* lse_cols = w + ws.lse_cols_off;
     void* delta_cols = w + ws.delta_cols_off;
     float* dq_accum = reinterpret_cast<float*>(w + ws.dq_accum_off);
+    float* delta_f32 = reinterpret_cast<float*>(w + ws.delta_f32_off);
+    // The dQ path.  Default: fp32 TMA reduce-add of the main kernel's dQ tiles into the accumulator: measured faster
+    // than the separate query-parallel pass at every benchmark shape (1.3-1.7x), and so is its ordered (deterministic)
+    // form except at one shape, so the separate pass is taken only when asked for.
+    const bool dq_separate = (flags & GQA_BWD_DQ_SEPARATE) != 0;
     unsigned int* dq_turn = nullptr;
-    if (flags & GQA_BWD_DETERMINISTIC) {
+    if ((flags & GQA_BWD_DETERMINISTIC) && !dq_separate) {
         dq_turn = reinterpret_cast<unsigned int*>(w + ws.dq_turn_off);
         GQA_CUDA_TRY(cudaMemsetAsync(dq_turn, 0, ws.dq_turn_bytes, stream));
     }
 
     GQA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, stream));
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[0], stream));
-    rc = gqa::launch_bwd_preprocess(O, dO, LSE, 1.0f / scale, nullptr, lse_cols, delta_cols, dq_accum, s.q_rows(), D,
-                                    stream, s.bshd ? S : 0, s.bshd ? Hq : 0);
+    rc = gqa::launch_bwd_preprocess(O, dO, LSE, 1.0f / scale, dq_separate ? delta_f32 : nullptr, lse_cols, delta_cols,
+                                    dq_separate ? nullptr : dq_accum, s.q_rows(), D, stream, s.bshd ? S : 0,
+                                    s.bshd ? Hq : 0);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[1], stream));
     float* partial = parts > 1 ? reinterpret_cast<float*>(w + ws.partial_off) : nullptr;
-    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_accum, dq_turn, dK, dV, s, status, parts,
-                                    partial, stream);
+    rc = gqa::launch_bwd_main_sm100(Q, K, V, dO, lse_cols, delta_cols, dq_separate ? nullptr : dq_accum, dq_turn, dK, dV,
+                                    s, status, parts, partial, stream);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[2], stream));
     if (parts > 1) {
         rc = gqa::launch_dkdv_reduce(partial, dK, dV, s, parts, stream);
         if (rc) return rc;
     }
-    rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows(), scale, stream, D, s.bshd ? S : 0, s.bshd ? Hq : 0);
+    if (dq_separate)
+        rc = gqa::launch_bwd_dq_sm100(Q, K, V, dO, LSE, delta_f32, dQ, s, status, stream);
+    else
+        rc = gqa::launch_dq_finalise(dq_accum, dQ, s.q_rows(), scale, stream, D, s.bshd ? S : 0, s.bshd ? Hq : 0);
     if (rc) return rc;
     if (ev) GQA_CUDA_TRY(cudaEventRecord(ev[3], stream));
     return GQA_OK;

@@ -156,7 +156,9 @@ __device__ __forceinline__ uint32_t p_col_of_kstep(int kk) {
     else return Cfg::kColP + kk * 8;
 }
 
-template <int D>
+// kWithDQ = false: the variant that leaves dQ to the separate query-parallel pass (gqa_bwd_dq_sm100.cu): no dQ
+// product, idle drain warps, and at D = 64 no dS^T in shared memory at all (dK reads its copy in TMEM).
+template <int D, bool kWithDQ>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
@@ -351,7 +353,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             GQA_TRACE(1, it, 1);
             ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 24);
             if (ok && it > 0) ok = mbar_wait(ds_ready, (it - 1) & 1, ctx, 25);                       // dP^T columns read
-            if (ok && it > 0 && Cfg::kDqAliasesDp) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);  // dQ drained
+            if (ok && it > 0 && Cfg::kDqAliasesDp && kWithDQ) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);  // dQ drained
             if (ok && it > 0 && Cfg::kDsInTmem)                                                      // dK read dS^T
                 ok = mbar_wait(&dk_done[(it - 1) % Cfg::kQStages], ((it - 1) / Cfg::kQStages) & 1, ctx, 27);
             if (!ok) break;
@@ -406,7 +408,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             }
             umma_commit_pred(leader, &dk_done[qs]);
             GQA_TRACE(4, it, 1);
-            {  // dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major)
+            if constexpr (!kWithDQ) {
+                umma_commit_pred(leader, ds_free);  // dK(it) was the last reader of dS^T(it)
+            } else {  // dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major)
                 if (it > 0) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 36);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -422,6 +426,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
         if (ok) umma_commit_pred(leader, acc_full);
     } else if (warp < kWarpEw0) {
+        if constexpr (kWithDQ) {
         // ======================= dQ drain warps =======================
         // Each warp owns 32 query rows: TMEM -> registers -> its own swizzled staging boxes -> TMA reduce-add
         // into the fp32 accumulator.  The reductions run on the copy engine, off the load/store pipe.
@@ -557,6 +562,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         release_held();
         if (lane == 0) bulk_wait_all();
         if (warp == 0) GQA_MARK(8);
+        }
     } else if (warp < Cfg::kWarpTma) {
         // ======================= elementwise warpgroups (P^T and dS^T) =======================
         // Rotated by half an iteration: the body of iteration `it` turns dP^T(it) into dS^T(it) and then
@@ -618,7 +624,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 }
                 const uint4 o = make_uint4(o4[0], o4[1], o4[2], o4[3]);
                 const int chunk = chunk0 + hf * 2 + q2;
-                *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
+                // shared-memory copy: read by dQ, and by dK where it does not have the TMEM copy
+                if constexpr (kWithDQ || !Cfg::kDsInTmem) *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) = o;
                 dsp[q2 * 4 + 0] = o.x;
                 dsp[q2 * 4 + 1] = o.y;
                 dsp[q2 * 4 + 2] = o.z;
@@ -680,7 +687,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     tmem_wait_st();
                 }
             }
-            fence_proxy_async_smem();
+            if constexpr (kWithDQ || !Cfg::kDsInTmem) fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(ds_ready);
             if (trace_me) GQA_TRACE(0, it, 1);
@@ -768,6 +775,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     }
 }
 
+// dq_accum == nullptr selects the variant without the dQ part.
 template <int D>
 int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
                  const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV, const Shape& s,
@@ -787,16 +795,18 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     if (rc) return rc;
     rc = make_tile3_tmap(&mdo, dO, qc, S, nq, S * qc, kTile);
     if (rc) return rc;
-    CUtensorMap mdq;
-    rc = make_f32box3_tmap(&mdq, dq_accum, D, S, nws, 32);
-    if (rc) return rc;
     CUtensorMap mlse, mdlt;
     rc = make_col8_3_tmap(&mlse, lse_cols, S, nws, kTile);
     if (rc) return rc;
     rc = make_col8_3_tmap(&mdlt, delta_cols, S, nws, kTile);
     if (rc) return rc;
-    GQA_CUDA_TRY(cudaFuncSetAttribute(gqa_bwd_sm100_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      Cfg::kSmemTotal));
+    CUtensorMap mdq = mlse;  // unused without the dQ part
+    if (dq_accum) {
+        rc = make_f32box3_tmap(&mdq, dq_accum, D, S, nws, 32);
+        if (rc) return rc;
+    }
+    auto kernel = dq_accum ? gqa_bwd_sm100_kernel<D, true> : gqa_bwd_sm100_kernel<D, false>;
+    GQA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemTotal));
     BwdParams p;
     p.dq_accum = dq_accum;
     p.dK = static_cast<__nv_bfloat16*>(dK);
@@ -816,7 +826,7 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)(p.n_tiles * s.B * s.Hkv * parts);
-    gqa_bwd_sm100_kernel<D><<<grid, Cfg::kThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, mlse, mdlt, p);
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, mlse, mdlt, p);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
     return GQA_OK;

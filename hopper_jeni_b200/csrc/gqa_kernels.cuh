@@ -27,14 +27,16 @@ struct BwdWorkspace {
     // -Delta in the first three, zeros after; they enter the S^T and dP^T products as one extra K step.
     // dq_turn: one counter per 32-row slice of a query tile, used only by the deterministic mode (order of the dQ
     // reductions).
-    size_t status_off, lse_cols_off, delta_cols_off, dq_turn_off, dq_turn_bytes, dq_accum_off, partial_off, partial_bytes,
-        total;
+    // delta_f32: Delta as fp32, one per query row, for the separate dQ pass (which subtracts it in registers).
+    size_t status_off, lse_cols_off, delta_cols_off, delta_f32_off, dq_turn_off, dq_turn_bytes, dq_accum_off, partial_off,
+        partial_bytes, total;
     explicit BwdWorkspace(const Shape& s, int parts = 1) {
         auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
         status_off = 0;
         lse_cols_off = 256;
         delta_cols_off = lse_cols_off + up(s.q_rows() * 16);
-        dq_turn_off = delta_cols_off + up(s.q_rows() * 16);
+        delta_f32_off = delta_cols_off + up(s.q_rows() * 16);
+        dq_turn_off = delta_f32_off + up(s.q_rows() * sizeof(float));
         dq_turn_bytes = (size_t)s.B * s.Hq * ((s.S + 127) / 128) * 4 * sizeof(unsigned int);  // per tile and drain warp
         dq_accum_off = dq_turn_off + up(dq_turn_bytes);
         partial_off = dq_accum_off + up(s.q_rows() * (size_t)s.Dp() * sizeof(float));  // accumulator rows are Dp wide
@@ -62,12 +64,17 @@ int launch_fwd_sm100(const void* Q, const void* K, const void* V, void* O, float
 // Stage 2 of the backward: KV-tile-parallel main kernel (tcgen05 + TMEM + TMA); dK/dV written
 // once per element, dQ accumulated into dq_accum with fp32 reductions.
 // With dq_turn (zeroed counters, one per 32 query rows) the reductions of every dQ tile are applied in KV-tile
-// order, which makes dQ bit-reproducible; nullptr = unordered.
+// order, which makes dQ bit-reproducible; nullptr = unordered.  dq_accum == nullptr launches the variant without the
+// dQ part (dK and dV only), for use with launch_bwd_dq_sm100.
 // With parts > 1 (a divisor of G) every KV tile is handled by `parts` thread blocks over disjoint query heads; their
 // fp32 dK / dV sums go to `partial` (BwdWorkspace::partial_bytes) and launch_dkdv_reduce adds them in a fixed order.
 int launch_bwd_main_sm100(const void* Q, const void* K, const void* V, const void* dO, const void* lse_cols,
                           const void* delta_cols, float* dq_accum, unsigned int* dq_turn, void* dK, void* dV,
                           const Shape& s, unsigned int* status, int parts, float* partial, cudaStream_t stream);
+// The alternative dQ path: a separate query-parallel pass that recomputes S and dP and writes dQ once (no accumulator,
+// no finalise, bit-reproducible).  `delta` is rowsum(dO * O) as fp32 per query row.
+int launch_bwd_dq_sm100(const void* Q, const void* K, const void* V, const void* dO, const float* lse,
+                        const float* delta, void* dQ, const Shape& s, unsigned int* status, cudaStream_t stream);
 // dK, dV = bf16(sum over the parts of the fp32 partial sums), in part order: the counterpart of gqa_dkdv_greduce
 // (src/attention/GQA_bwd_baseline.cu:385-403), on fp32 partials and only when the head split is in use.
 int launch_dkdv_reduce(const float* partial, void* dK, void* dV, const Shape& s, int parts, cudaStream_t stream);

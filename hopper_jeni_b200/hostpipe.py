@@ -18,24 +18,25 @@ from . import ops, sharding
 
 
 class HostBackward:
-    def __init__(self, B, Hq, Hkv, S, D, causal=False, scale=None, chunks=8, device=None):
+    def __init__(self, B, Hq, Hkv, S, D, causal=False, scale=None, chunks=8, device=None, n_slots=2):
         self.shape = (B, Hq, Hkv, S, D)
         self.causal = bool(causal)
         self.scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         n_groups = B * Hkv
-        self.chunks = max(1, min(int(chunks), n_groups))
-        self.ranges = [sharding.group_range(c, self.chunks, n_groups) for c in range(self.chunks)]
+        n_chunks = max(1, min(int(chunks), n_groups))
+        self.ranges = [sharding.group_range(c, n_chunks, n_groups) for c in range(n_chunks)]
+        self.chunks = len(self.ranges)
         g_max = max(e - b for b, e in self.ranges)
         G = Hq // Hkv
         dev, bf, f32 = self.device, torch.bfloat16, torch.float32
         mk = lambda *s, dt=bf: torch.empty(s, dtype=dt, device=dev)
-        # two staging slots: inputs, outputs and a workspace each
+        # staging slots (two by default): inputs, outputs and a workspace each
         self.slots = [dict(q=mk(g_max, G, S, D), k=mk(g_max, 1, S, D), v=mk(g_max, 1, S, D), o=mk(g_max, G, S, D),
                            do=mk(g_max, G, S, D), lse=mk(g_max, G, S, dt=f32), dq=mk(g_max, G, S, D),
                            dk=mk(g_max, 1, S, D), dv=mk(g_max, 1, S, D),
                            ws=torch.empty(ops.bwd_workspace_bytes(g_max, G, 1, S, D, causal), dtype=torch.uint8,
-                                          device=dev)) for _ in range(2)]
+                                          device=dev)) for _ in range(max(2, int(n_slots)))]
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
         self.h2d_bytes = (3 * B * Hq * S * D + 2 * B * Hkv * S * D) * 2 + B * Hq * S * 4
         self.d2h_bytes = (B * Hq * S * D + 2 * B * Hkv * S * D) * 2
@@ -53,17 +54,18 @@ class HostBackward:
         computed = [torch.cuda.Event() for _ in self.ranges]
         drained = [torch.cuda.Event() for _ in self.ranges]
         for c, (b, e) in enumerate(self.ranges):
-            slot, n = self.slots[c & 1], e - b
+            ns = len(self.slots)
+            slot, n = self.slots[c % ns], e - b
             with torch.cuda.stream(self.s_in):
-                if c >= 2:
-                    self.s_in.wait_event(computed[c - 2])   # the slot's inputs were consumed
+                if c >= ns:
+                    self.s_in.wait_event(computed[c - ns])   # the slot's inputs were consumed
                 for name, h in zip(("q", "k", "v", "o", "do", "lse"), hin):
                     slot[name][:n].copy_(h[b:e], non_blocking=True)
                 copied[c].record(self.s_in)
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(copied[c])
-                if c >= 2:
-                    self.s_run.wait_event(drained[c - 2])   # the slot's outputs were copied out
+                if c >= ns:
+                    self.s_run.wait_event(drained[c - ns])   # the slot's outputs were copied out
                 ops.gqa_backward(slot["q"][:n], slot["k"][:n], slot["v"][:n], slot["o"][:n], slot["do"][:n],
                                  slot["lse"][:n], causal=self.causal, scale=self.scale, workspace=slot["ws"],
                                  dq=slot["dq"][:n], dk=slot["dk"][:n], dv=slot["dv"][:n], stream=self.s_run)

@@ -90,12 +90,13 @@ def bwd_workspace_bytes(B, Hq, Hkv, S, D, causal=False, split_heads: bool = Fals
 
 def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None = None,
                  workspace=None, dq=None, dk=None, dv=None, stream=None, deterministic: bool = False,
-                 layout: str = "bhsd", split_heads: bool = False):
+                 layout: str = "bhsd", split_heads: bool = False, dq_separate: bool = False):
     """dQ, dK, dV.  Mirrors ``launch_gqa_backward_vj1d`` (G derived from the head counts).
     ``deterministic`` orders the dQ reductions (``GQA_BWD_DETERMINISTIC``): bit-reproducible dQ, slower.
     ``layout="bshd"``: all bf16 tensors are [B,S,H,D] (``GQA_LAYOUT_BSHD``); LSE is [B,Hq,S] either way.
     ``split_heads`` (``GQA_BWD_SPLIT_HEADS``): let a call with few KV tiles cut each tile's work over several thread
-    blocks by query head (fp32 partial dK/dV, fixed-order sum); the workspace must be sized with the same option."""
+    blocks by query head (fp32 partial dK/dV, fixed-order sum); the workspace must be sized with the same option.
+    ``dq_separate`` (``GQA_BWD_DQ_SEPARATE``): dQ from a separate query-parallel pass instead of the accumulator."""
     lib = capi.load_library()
     for t, n in ((q, "Q"), (k, "K"), (v, "V"), (o, "O"), (do, "dO")):
         _req(t, n, torch.bfloat16)
@@ -124,7 +125,7 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, S, D, int(bool(causal)), scale,
                 workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream_ptr(stream))
         flags = ((capi.GQA_BWD_DETERMINISTIC if deterministic else 0) | (capi.GQA_LAYOUT_BSHD if layout == "bshd" else 0)
-                 | (capi.GQA_BWD_SPLIT_HEADS if split_heads else 0))
+                 | (capi.GQA_BWD_SPLIT_HEADS if split_heads else 0) | (capi.GQA_BWD_DQ_SEPARATE if dq_separate else 0))
         rc = lib.gqa_bwd_ex(*args, flags) if flags else lib.gqa_bwd(*args)
     capi.check("gqa_bwd_ex" if flags else "gqa_bwd", rc)
     return dq, dk, dv

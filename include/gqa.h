@@ -115,9 +115,16 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
  * makespan); dK and dV stay bit-reproducible from run to run, but their last bits depend on the split, so results
  * are no longer bit-identical across different shardings of one problem, which is why this is a flag.  The
  * workspace must come from gqa_bwd_workspace_bytes_ex with the same flags.
+ * GQA_BWD_DQ_SEPARATE: compute dQ in a separate query-parallel pass (one thread block per 128-row query tile looping
+ * over the key tiles, as the reference's first generations do, src/attention/GQA_bwd.cu:29, :415, :1416) instead
+ * of accumulating the main kernel's dQ tiles with fp32 reductions.  S and dP are then computed twice, but dQ needs
+ * no accumulator, no finalise pass, and is bit-reproducible by construction.  Measured 1.3-1.7x slower than the
+ * default at the benchmark shapes, and slower than GQA_BWD_DETERMINISTIC's ordered reductions at all of them but one
+ * (B4 Hq32 Hkv8 S8192 D128 causal: 7.7 against 8.6 ms), so no mode selects it by itself.  Same workspace size.
  */
 #define GQA_BWD_DETERMINISTIC 1u
 #define GQA_BWD_SPLIT_HEADS 4u
+#define GQA_BWD_DQ_SEPARATE 8u
 size_t gqa_bwd_workspace_bytes_ex(int B, int Hq, int Hkv, int S, int D, int causal, unsigned int flags);
 int gqa_bwd_ex(const void* Q, const void* K, const void* V, const void* O, const void* dO,
                const float* LSE, void* dQ, void* dK, void* dV,
@@ -139,7 +146,7 @@ int gqa_bwd_ex(const void* Q, const void* K, const void* V, const void* O, const
  *
  *  - Shapes whose scratch (gqa_bwd_workspace_bytes) exceeds the array are refused with
  *    GQA_ERR_WORKSPACE and an explanation in gqa_last_cuda_error(); nothing is launched.
- *    32 MiB covers e.g. B*Hq*S <= 114 688 rows at D = 64 or 61 440 rows at D = 128.
+ *    32 MiB covers e.g. B*Hq*S <= 114 000 rows at D <= 64 or 61 000 rows at D <= 128.
  *  - It calls no cudaMalloc/cudaFree and no allocating library routine.
  *  - The first call on each device looks up the array's device address (one runtime
  *    query, no allocation).  Make that first call outside any stream capture.
