@@ -5,6 +5,11 @@
 //   * finalise:   dQ = bf16(scale * dq_accum) (stage 3).
 // Algorithmic traffic per query row (D bf16 elements): preprocess reads 2*D*2 B and writes
 // D*4 + 32 B; finalise reads D*4 B and writes D*2 B.
+#include <algorithm>
+#include <functional>
+#include <queue>
+#include <vector>
+
 #include "gqa_common.cuh"
 #include "gqa_kernels.cuh"
 
@@ -192,23 +197,29 @@ int bwd_head_parts(const Shape& s) {
     const int G = s.G(), n_tiles = (s.S + 127) / 128;
     const long items = (long)n_tiles * s.B * s.Hkv;
     if (G == 1 || s.bshd || items >= 2 * kSms) return 1;
+    // This runs on the host in front of every call that passes the flag: the answer for the last shape is kept.
+    static thread_local int memo_key[6] = {-1, -1, -1, -1, -1, -1}, memo_parts = 1;
+    const int key[6] = {s.B, s.Hq, s.Hkv, s.S, s.D, s.causal};
+    if (std::equal(key, key + 6, memo_key)) return memo_parts;
     // Estimated makespan (in tile pairs) of list scheduling, longest item first, on the SMs, for every divisor of G;
     // every item also pays a fixed start/finish cost worth about four tile pairs.  The split is taken only when it
     // shortens the estimate by more than 8 %: the partial sums and their reduction are not free.
-    auto makespan = [&](int parts) {
-        double load[kSms] = {};
+    auto makespan = [&](int parts) -> double {
         const int g_local = G / parts;
+        const long per_tile = (long)s.B * s.Hkv * parts;  // items of equal length
+        if (!s.causal) return (double)((items * parts + kSms - 1) / kSms) * (g_local * n_tiles + 4.0);
+        std::priority_queue<double, std::vector<double>, std::greater<double>> load;  // the least loaded SM on top
+        for (int i = 0; i < kSms; ++i) load.push(0.0);
+        double worst = 0;
         for (int kt = 0; kt < n_tiles; ++kt) {
-            const double len = (double)g_local * (s.causal ? n_tiles - kt : n_tiles) + 4.0;
-            for (long rep = 0; rep < (long)s.B * s.Hkv * parts; ++rep) {
-                int best = 0;
-                for (int i = 1; i < kSms; ++i)
-                    if (load[i] < load[best]) best = i;
-                load[best] += len;
+            const double len = (double)g_local * (n_tiles - kt) + 4.0;
+            for (long rep = 0; rep < per_tile; ++rep) {
+                const double l = load.top() + len;
+                load.pop();
+                load.push(l);
+                worst = l > worst ? l : worst;
             }
         }
-        double worst = 0;
-        for (double l : load) worst = l > worst ? l : worst;
         return worst;
     };
     int best_parts = 1;
@@ -221,6 +232,8 @@ int bwd_head_parts(const Shape& s) {
             best_parts = parts;
         }
     }
+    std::copy(key, key + 6, memo_key);
+    memo_parts = best_parts;
     return best_parts;
 }
 
