@@ -103,7 +103,11 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
  * (cp.reduce.async.bulk add, src/attention/GQA_bwd_baseline.cu:360-365, run-to-run differences noted in
  * docs/report.md:115-116) and has no such switch; its determinism probe
  * (precision/vj1d_determinism_probe.cu:33) is what this mode is checked with.  Slower than the default
- * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.
+ * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.  A thread
+ * block waits for the turn of the block that owns the previous KV tile of its group, which has a smaller block
+ * index: the mode relies on the hardware starting thread blocks in index order (it does on every CUDA GPU so far,
+ * but CUDA does not promise it); the wait is bounded, so a violation would end in GQA_ERR_DEVICE_TIMEOUT, not in
+ * a hang.
  * GQA_LAYOUT_BSHD (see gqa_fwd_ex): Q, O, dO, dQ are [B,S,Hq,D] and K, V, dK, dV [B,S,Hkv,D]; LSE stays [B,Hq,S].
  * Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
  * GQA_BWD_SPLIT_HEADS: for calls with too few KV tiles to fill the GPU evenly (fewer than two per SM: a
