@@ -35,6 +35,8 @@
 // roundings follow the reference: P is rounded to bf16 before dV and before the dS product,
 // dS = bf16(P_bf16 * (dP - Delta)) with the product in fp32, dK and dQ are scaled in fp32
 // (GQA_bwd_baseline.cu:243-255, :320-326, :530-534).
+#include <type_traits>
+
 #include "gqa_common.cuh"
 #include "gqa_kernels.cuh"
 #include "sm100_ptx.cuh"
@@ -51,6 +53,30 @@ using namespace sm100;
 #endif
 __device__ long long g_bwd_trace[5][64][4];
 __device__ long long g_bwd_marks[16];
+__device__ long long g_bwd_items[4096][6];  // per work item: block, SM, start and end (globaltimer, ns), start and end (clock64)
+__device__ __forceinline__ long long trace_globaltimer() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ int trace_smid() {
+    int v;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+    return v;
+}
+#define GQA_ITEM_BEGIN(idx)                                  \
+    do {                                                     \
+        if ((idx) < 4096) {                                  \
+            g_bwd_items[idx][0] = blockIdx.x;                \
+            g_bwd_items[idx][1] = trace_smid();              \
+            g_bwd_items[idx][2] = trace_globaltimer();       \
+            g_bwd_items[idx][4] = clock64();                 \
+        }                                                    \
+    } while (0)
+#define GQA_ITEM_END(idx)                                          \
+    do {                                                           \
+        if ((idx) < 4096) { g_bwd_items[idx][3] = trace_globaltimer(); g_bwd_items[idx][5] = clock64(); } \
+    } while (0)
 #define GQA_MARK(slot)                                                                            \
     do {                                                                                           \
         if (blockIdx.x == GQA_BWD_TRACE_BLOCK && (threadIdx.x & 31) == 0) g_bwd_marks[slot] = clock64(); \
@@ -65,6 +91,12 @@ __device__ long long g_bwd_marks[16];
     } while (0)
 #define GQA_MARK(slot) \
     do {               \
+    } while (0)
+#define GQA_ITEM_BEGIN(idx) \
+    do {                    \
+    } while (0)
+#define GQA_ITEM_END(idx) \
+    do {                  \
     } while (0)
 #endif
 
@@ -111,7 +143,7 @@ struct BwdCfg {
     static constexpr int kOffDltCol = kOffLseCol + kQStages * kColPanel;  // [kDOStages] -Delta columns
     static constexpr int kOffZero = kOffDltCol + kDOStages * kColPanel;   // all-zero panel (columns 8-15 of every one)
     static constexpr int kOffBars = kOffZero + kColPanel;
-    static constexpr int kSmemTotal = kOffBars + 256;  // the dynamic window must start 1024-byte aligned (checked)
+    static constexpr int kSmemTotal = kOffBars + 384;  // the dynamic window must start 1024-byte aligned (checked)
     static constexpr uint32_t kTmemCols = 512;
     // fp32 column map.  D = 64: every tile has its own columns.  D = 128: P^T overwrites the S^T columns
     // and dQ reuses the dP^T columns; the p_free / dq_empty barriers guard the reuse.
@@ -142,6 +174,9 @@ struct BwdParams {
     // few KV tiles to fill the SMs evenly (a long-context problem sharded down to one KV head per GPU).
     float* partial;
     int parts;
+    int groups;   // B * Hkv
+    int sg;       // causal order: (batch, KV head) groups per super-group (see the work-item comment)
+    int n_items;  // n_tiles * groups * parts: work items, each handled by one thread block at a time
     int Hq, Hkv, S, causal, n_tiles, G, bshd;
     int d_real;  // head dimension of the tensors (<= D of the kernel; the columns beyond it read as zeros)
     float scale, scale_log2;
@@ -191,49 +226,99 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     uint64_t* ds_ready = bars + 2;   // elementwise -> issuers: dS^T(it) stored, dP^T(it) consumed
     uint64_t* ds_free = bars + 3;    // after dQ(it) (covers dK(it), same thread): dS^T(it) consumed, dQ(it) complete
     uint64_t* dq_empty = bars + 4;   // drain warps -> issuers: dQ columns free
-    uint64_t* acc_full = bars + 5;   // issuers dV + dK after their last products -> epilogue
-    uint64_t* s_full = bars + 6;                     // [kQStages] after S^T(it): -> elementwise
+    uint64_t* acc_full = bars + 5;   // issuers dV + dK after the last products of a work item -> epilogue
+    uint64_t* acc_empty = bars + 6;  // elementwise -> issuers dV + dK: the accumulators of the item have been read
+    uint64_t* kv_empty = bars + 7;   // issuer dK/dQ after the last product of an item: K and V may be overwritten
+    uint64_t* s_full = bars + 8;                     // [kQStages] after S^T(it): -> elementwise
     uint64_t* dk_done = s_full + Cfg::kQStages;      // [kQStages] after dK(it): Q stage free (S^T(it) finished long before),
                                                      //            and the dS^T copy in the dP^T columns has been read
     uint64_t* q_full = dk_done + Cfg::kQStages;      // [kQStages] TMA: Q tile + -LSE/scale columns
     uint64_t* dp_full = q_full + Cfg::kQStages;      // [kDOStages] after dP^T(it): -> elementwise; dO stage read by dP^T
     uint64_t* p_free = dp_full + Cfg::kDOStages;     // [kDOStages] after dV(it): P^T(it) consumed; dO stage read by dV
     uint64_t* do_full = p_free + Cfg::kDOStages;     // [kDOStages] TMA: dO tile + -Delta columns
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(do_full + Cfg::kDOStages);
+    uint64_t* item_full = do_full + Cfg::kDOStages;  // [kItemSlots] TMA producer -> everybody: the block's next work item
+    constexpr int kItemSlots = 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(item_full + kItemSlots);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+    volatile int* item_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [kItemSlots]
+    static_assert((8 + 3 * Cfg::kQStages + 3 * Cfg::kDOStages + kItemSlots) * 8 + 8 + kItemSlots * 4 <= 384, "barrier area");
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
     AbortCtx ctx{abort_flag, p.status};
 
-    // ---- work decode.  Non-causal: the KV tiles of one (batch, KV head) group are neighbours in launch order,
-    // so the CTAs that run at the same time share their Q/dO tiles and dQ accumulator rows in L2 (measured
-    // +6.7 % at the headline shape).  Causal: the KV tile is the slow index so the longest items start first
-    // (load balance matters more there: measured +6 %). ----
-    const int groups = gridDim.x / (p.n_tiles * p.parts);  // B * Hkv
-    const int part = (int)blockIdx.x % p.parts, item = (int)blockIdx.x / p.parts;  // the parts of a tile are neighbours
-    // The deterministic mode also takes the KV tile as the slow index: the CTAs of one group that run at the same
-    // time must reduce one after the other, and this order keeps only a few of them in flight together.
+    // ---- work items.  The grid is persistent (one thread block per SM, fewer when there is less work).  A block
+    // starts with item blockIdx.x and then takes the next unclaimed item of the list below from a counter in global
+    // memory, one after the other, with every barrier and ring simply carrying on, so that the head of an item (K/V
+    // load, first S^T) overlaps the tail of the previous one (epilogue, last dQ drains).  The claim is dynamic and made
+    // late (see the producer), so that the items are handed out in list order as the blocks become free, like thread
+    // blocks by the hardware: neighbours in the list then run side by side and share their Q/dO tiles in L2.  A fixed
+    // share per block (items c, c + gridDim.x, ... in snake order) broke that and was 19 % slower at the 32k-token
+    // causal shape.  Launched with one block per item the same code is the classic one-item-per-block kernel and never
+    // touches the counter.
+    // Order of the list.  Non-causal: the KV tiles of one (batch, KV head) group are neighbours, so the blocks that
+    // run at the same time share their Q/dO tiles and dQ accumulator rows in L2 (measured +6.7 % at the headline
+    // shape).  Causal: super-groups of (batch, KV head) groups, inside them the KV tile is the slow index, longest items
+    // first (list scheduling in that order; the size of a super-group is chosen on the host).  The
+    // deterministic mode also takes the KV tile as the slow index: the blocks of one group that run at the same time
+    // must reduce one after the other, and this order keeps only a few of them in flight together.  It is launched
+    // with one block per item: its blocks wait for one another, and a block that waits must never hold the SM that
+    // the block it waits for needs (blocks are dispatched in index order, and a block only waits for lower ones).
+    struct WorkItem {
+        int kt, grp, part, b, hkv, qt0, n_qt, n_iter, kv_x, kv_z;
+        int shift;  // the item's loop over the query tiles of a head starts at tile qt0 + shift and wraps around
+    };
     const bool kt_major = p.causal || p.dq_turn != nullptr;
-    const int kt = kt_major ? item / groups : item % p.n_tiles;
-    const int grp = kt_major ? item % groups : item / p.n_tiles;
-    const int b = grp / p.Hkv, hkv = grp % p.Hkv;
-    const int qt0 = p.causal ? kt : 0;
-    const int n_qt = p.n_tiles - qt0;
-    const int g_local = p.G / p.parts;  // query heads this thread block loops over
-    const int n_iter = g_local * n_qt;
+    const int g_local = p.G / p.parts;  // query heads a work item loops over
+    // The j-th item of this block, published by the TMA producer in a small ring of slots; -1 = no more (or give up).
+    // A slot is rewritten four items later, when every role has long read it (the producer publishes item j after
+    // it has issued the loads of item j-1, which needs the products of item j-2 complete and with them the drains
+    // inside item j-3 at the least).
+    auto fetch_item = [&](int j) -> int {
+        if (!mbar_wait(&item_full[j & (kItemSlots - 1)], (j / kItemSlots) & 1, ctx, 14)) return -1;
+        return item_slot[j & (kItemSlots - 1)];
+    };
+    auto decode = [&](int idx) -> WorkItem {
+        WorkItem w;
+        w.part = idx % p.parts;  // the parts of a tile are neighbours
+        const int item = idx / p.parts;
+        if (kt_major) {  // super-group, then KV tile, then group inside the super-group
+            const int per_sg = p.n_tiles * p.sg;
+            const int r = item % per_sg;
+            w.kt = r / p.sg;
+            w.grp = (item / per_sg) * p.sg + r % p.sg;
+        } else {
+            w.kt = item % p.n_tiles;
+            w.grp = item / p.n_tiles;
+        }
+        w.b = w.grp / p.Hkv;
+        w.hkv = w.grp % p.Hkv;
+        w.qt0 = p.causal ? w.kt : 0;
+        w.n_qt = p.n_tiles - w.qt0;
+        w.n_iter = g_local * w.n_qt;
+        // Non-causal: the blocks of one (batch, KV head) group start together; rotated by their KV tile index they
+        // are on different query tiles at any time, so their dQ reductions do not queue on the same lines in L2 (all
+        // starting at tile 0, the first waves ran 10-15 % slower per tile pair than the later, drifted-apart ones).
+        // Causal blocks are staggered already (block kt starts at query tile kt); the deterministic mode wants its
+        // blocks on the same tile one after the other.
+        w.shift = kt_major ? 0 : w.kt;
+        w.kv_x = p.bshd ? w.hkv * D : 0;
+        w.kv_z = p.bshd ? w.b : w.b * p.Hkv + w.hkv;
+        return w;
+    };
     // Tensor-map coordinates (x = column, y = position in the sequence, z = matrix).  [B,H,S,D] is B*H matrices
     // [S, D]; [B,S,H,D] is B matrices [S, H*D] with the head at x = head * D.  The workspace arrays are B*Hq
     // matrices [S, .].  Rows at y >= S read as zeros and are skipped by the reductions, so S may be any length:
     // keys beyond S give zero rows of K and V (their dK / dV rows are not stored and their dS meets a zero row of
     // K in dQ), queries beyond S give zero rows of Q, dO and of the -LSE / -Delta columns (P = 1, dS = 0).
-    const int kv_x = p.bshd ? hkv * D : 0, kv_z = p.bshd ? b : b * p.Hkv + hkv;
-    auto head_of = [&](int it) { return hkv * p.G + part * g_local + it / n_qt; };  // query head inside the batch
-    auto q_y_of = [&](int it) { return (qt0 + it % n_qt) * kTile; };     // first query position of the tile
-    auto q_x_of = [&](int it) { return p.bshd ? head_of(it) * D : 0; };
-    auto q_z_of = [&](int it) { return p.bshd ? b : b * p.Hq + head_of(it); };
-    auto ws_z_of = [&](int it) { return b * p.Hq + head_of(it); };
+    auto head_of = [&](const WorkItem& w, int it) { return w.hkv * p.G + w.part * g_local + it / w.n_qt; };
+    auto q_y_of = [&](const WorkItem& w, int it) {  // first query position
+        return (w.qt0 + (it % w.n_qt + w.shift) % w.n_qt) * kTile;
+    };
+    auto q_x_of = [&](const WorkItem& w, int it) { return p.bshd ? head_of(w, it) * D : 0; };
+    auto q_z_of = [&](const WorkItem& w, int it) { return p.bshd ? w.b : w.b * p.Hq + head_of(w, it); };
+    auto ws_z_of = [&](const WorkItem& w, int it) { return w.b * p.Hq + head_of(w, it); };
 
     if (tid == 0) {
         // a thread block of this launch that has already given up leaves a non-zero status word: the blocks that
@@ -245,11 +330,14 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         mbar_init(ds_free, 1);
         mbar_init(dq_empty, 128);
         mbar_init(acc_full, 2);
+        mbar_init(acc_empty, Cfg::kEwThreads);
+        mbar_init(kv_empty, 1);
         for (int i = 0; i < Cfg::kQStages; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&dk_done[i], 1);
             mbar_init(&q_full[i], 1);
         }
+        for (int i = 0; i < kItemSlots; ++i) mbar_init(&item_full[i], 1);
         for (int i = 0; i < Cfg::kDOStages; ++i) {
             mbar_init(&dp_full[i], 1);
             mbar_init(&p_free[i], 1);
@@ -288,35 +376,65 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tma_prefetch_desc(&mapDQ);
             tma_prefetch_desc(&mapLseCol);
             tma_prefetch_desc(&mapDltCol);
-            mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
-            for (int pn = 0; pn < Cfg::kPanels; ++pn) {
-                tma_load_3d(sK + pn * kPanel, &mapK, kv_full, kv_x + pn * 64, kt * kTile, kv_z);
-                tma_load_3d(sV + pn * kPanel, &mapV, kv_full, kv_x + pn * 64, kt * kTile, kv_z);
-            }
-            for (int it = 0; it < n_iter; ++it) {
-                const int qx = q_x_of(it), qy = q_y_of(it), qz = q_z_of(it), wz = ws_z_of(it);
-                {
-                    const int st = it % Cfg::kQStages;
-                    const uint32_t use = it / Cfg::kQStages;
-                    // the stage's last reader is dK of its previous use
-                    if (use > 0 && !mbar_wait(&dk_done[st], (use - 1) & 1, ctx, 10)) break;
-                    // the -LSE/scale columns of the tile ride with Q (both are operands of S^T)
-                    mbar_expect_tx(&q_full[st], Cfg::kTileBytes + Cfg::kColPanel);
-                    for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                        tma_load_3d(sQ + st * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[st], qx + pn * 64, qy, qz);
-                    tma_load_3d(sLseCol + st * Cfg::kColPanel, &mapLseCol, &q_full[st], 0, qy, wz);
+            unsigned int* work_counter = p.status + 16;  // zeroed with the status word before every launch
+            int gi = 0;  // iterations issued so far, over all items: the rings and their barriers carry on across items
+            int idx = blockIdx.x;
+            bool ok = true;
+            for (int j = 0; ok; ++j) {
+                item_slot[j & (kItemSlots - 1)] = idx;
+                mbar_arrive(&item_full[j & (kItemSlots - 1)]);
+                if (idx < 0) break;
+                const WorkItem w = decode(idx);
+                if (j > 0) {
+                    // a block of this launch that gave up has left a non-zero status word: stop taking items
+                    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0u) {
+                        *abort_flag = 98u;
+                        break;
+                    }
+                    if (!mbar_wait(kv_empty, (j - 1) & 1, ctx, 13)) break;  // the previous item's last readers of K, V
                 }
-                {
-                    const int st = it % Cfg::kDOStages;
-                    const uint32_t use = it / Cfg::kDOStages;
-                    // the stage's readers are dP^T and dV of its previous use (neither implies the other)
-                    if (use > 0 && !(mbar_wait(&dp_full[st], (use - 1) & 1, ctx, 11) && mbar_wait(&p_free[st], (use - 1) & 1, ctx, 12))) break;
-                    // the -Delta columns ride with dO (both are operands of dP^T)
-                    mbar_expect_tx(&do_full[st], Cfg::kTileBytes + Cfg::kColPanel);
-                    for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                        tma_load_3d(sDO + st * Cfg::kTileBytes + pn * kPanel, &mapDO, &do_full[st], qx + pn * 64, qy, qz);
-                    tma_load_3d(sDltCol + st * Cfg::kColPanel, &mapDltCol, &do_full[st], 0, qy, wz);
+                mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+                for (int pn = 0; pn < Cfg::kPanels; ++pn) {
+                    tma_load_3d(sK + pn * kPanel, &mapK, kv_full, w.kv_x + pn * 64, w.kt * kTile, w.kv_z);
+                    tma_load_3d(sV + pn * kPanel, &mapV, kv_full, w.kv_x + pn * 64, w.kt * kTile, w.kv_z);
                 }
+                int next = -1;
+                for (int it = 0; it < w.n_iter; ++it, ++gi) {
+                    // Claim the next item while the last tile pair of this one is loaded: late, so that the items
+                    // are handed out in the order in which the blocks become free, as the hardware hands out thread
+                    // blocks (neighbouring items then run side by side and share their Q/dO tiles in L2: claimed a
+                    // whole item early, the 32k-token causal shape went to HBM for them, drew 13 % more energy
+                    // per tile pair and ran that much slower under the power cap); the round trip to the counter hides
+                    // behind the tile pairs that are still in the rings.
+                    if (it == w.n_iter - 1 && (int)gridDim.x < p.n_items) {
+                        next = (int)gridDim.x + (int)atomicAdd(work_counter, 1u);
+                        if (next >= p.n_items) next = -1;
+                    }
+                    const int qx = q_x_of(w, it), qy = q_y_of(w, it), qz = q_z_of(w, it), wz = ws_z_of(w, it);
+                    {
+                        const int st = gi % Cfg::kQStages;
+                        const uint32_t use = gi / Cfg::kQStages;
+                        // the stage's last reader is dK of its previous use
+                        if (use > 0 && !mbar_wait(&dk_done[st], (use - 1) & 1, ctx, 10)) { ok = false; break; }
+                        // the -LSE/scale columns of the tile ride with Q (both are operands of S^T)
+                        mbar_expect_tx(&q_full[st], Cfg::kTileBytes + Cfg::kColPanel);
+                        for (int pn = 0; pn < Cfg::kPanels; ++pn)
+                            tma_load_3d(sQ + st * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[st], qx + pn * 64, qy, qz);
+                        tma_load_3d(sLseCol + st * Cfg::kColPanel, &mapLseCol, &q_full[st], 0, qy, wz);
+                    }
+                    {
+                        const int st = gi % Cfg::kDOStages;
+                        const uint32_t use = gi / Cfg::kDOStages;
+                        // the stage's readers are dP^T and dV of its previous use (neither implies the other)
+                        if (use > 0 && !(mbar_wait(&dp_full[st], (use - 1) & 1, ctx, 11) && mbar_wait(&p_free[st], (use - 1) & 1, ctx, 12))) { ok = false; break; }
+                        // the -Delta columns ride with dO (both are operands of dP^T)
+                        mbar_expect_tx(&do_full[st], Cfg::kTileBytes + Cfg::kColPanel);
+                        for (int pn = 0; pn < Cfg::kPanels; ++pn)
+                            tma_load_3d(sDO + st * Cfg::kTileBytes + pn * kPanel, &mapDO, &do_full[st], qx + pn * 64, qy, qz);
+                        tma_load_3d(sDltCol + st * Cfg::kColPanel, &mapDltCol, &do_full[st], 0, qy, wz);
+                    }
+                }
+                idx = next;
             }
         }
     } else if (warp == Cfg::kWarpMmaS) {
@@ -338,93 +456,119 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             umma_ss_pred(leader, tmem + col, ones_desc, make_sdesc_noswizzle(cols_addr, zero_addr - cols_addr, 128), idesc,
                          1u);
         };
-        bool ok = mbar_wait(kv_full, 0, ctx, 20);
-        for (int it = 0; it < n_iter && ok; ++it) {
-            const int qs = it % Cfg::kQStages, dos = it % Cfg::kDOStages;
-            ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 21);
-            if (ok && it > 0) ok = mbar_wait(p_ready, (it - 1) & 1, ctx, 22);                        // S^T columns read
-            if (ok && it > 0 && Cfg::kPAliasesS)                                                     // P^T consumed
-                ok = mbar_wait(&p_free[(it - 1) % Cfg::kDOStages], ((it - 1) / Cfg::kDOStages) & 1, ctx, 23);
-            if (!ok) break;
-            tc_fence_after_sync();
-            GQA_TRACE(1, it, 0);
-            issue(Cfg::kColS, k_addr, q_addr + qs * Cfg::kTileBytes, smem_u32(sLseCol) + qs * Cfg::kColPanel);
-            umma_commit_pred(leader, &s_full[qs]);
-            GQA_TRACE(1, it, 1);
-            ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 24);
-            if (ok && it > 0) ok = mbar_wait(ds_ready, (it - 1) & 1, ctx, 25);                       // dP^T columns read
-            if (ok && it > 0 && Cfg::kDqAliasesDp && kWithDQ) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 26);  // dQ drained
-            if (ok && it > 0 && Cfg::kDsInTmem)                                                      // dK read dS^T
-                ok = mbar_wait(&dk_done[(it - 1) % Cfg::kQStages], ((it - 1) / Cfg::kQStages) & 1, ctx, 27);
-            if (!ok) break;
-            tc_fence_after_sync();
-            GQA_TRACE(1, it, 2);
-            issue(Cfg::kColDP, v_addr, do_addr + dos * Cfg::kTileBytes, smem_u32(sDltCol) + dos * Cfg::kColPanel);
-            umma_commit_pred(leader, &dp_full[dos]);
-            GQA_TRACE(1, it, 3);
+        int gi = 0;  // iteration index over all items of this block (parities and ring stages carry on across items)
+        bool ok = true;
+        for (int j = 0; ok; ++j) {
+            const int idx = fetch_item(j);
+            if (idx < 0) break;
+            const int n_iter = decode(idx).n_iter;
+            ok = mbar_wait(kv_full, j & 1, ctx, 20);
+            for (int it = 0; it < n_iter && ok; ++it, ++gi) {
+                const int qs = gi % Cfg::kQStages, dos = gi % Cfg::kDOStages;
+                ok = mbar_wait(&q_full[qs], (gi / Cfg::kQStages) & 1, ctx, 21);
+                if (ok && gi > 0) ok = mbar_wait(p_ready, (gi - 1) & 1, ctx, 22);                        // S^T columns read
+                if (ok && gi > 0 && Cfg::kPAliasesS)                                                     // P^T consumed
+                    ok = mbar_wait(&p_free[(gi - 1) % Cfg::kDOStages], ((gi - 1) / Cfg::kDOStages) & 1, ctx, 23);
+                if (!ok) break;
+                tc_fence_after_sync();
+                GQA_TRACE(1, gi, 0);
+                issue(Cfg::kColS, k_addr, q_addr + qs * Cfg::kTileBytes, smem_u32(sLseCol) + qs * Cfg::kColPanel);
+                umma_commit_pred(leader, &s_full[qs]);
+                GQA_TRACE(1, gi, 1);
+                ok = mbar_wait(&do_full[dos], (gi / Cfg::kDOStages) & 1, ctx, 24);
+                if (ok && gi > 0) ok = mbar_wait(ds_ready, (gi - 1) & 1, ctx, 25);                       // dP^T columns read
+                if (ok && gi > 0 && Cfg::kDqAliasesDp && kWithDQ) ok = mbar_wait(dq_empty, (gi - 1) & 1, ctx, 26);  // dQ drained
+                if (ok && gi > 0 && Cfg::kDsInTmem)                                                      // dK read dS^T
+                    ok = mbar_wait(&dk_done[(gi - 1) % Cfg::kQStages], ((gi - 1) / Cfg::kQStages) & 1, ctx, 27);
+                if (!ok) break;
+                tc_fence_after_sync();
+                GQA_TRACE(1, gi, 2);
+                issue(Cfg::kColDP, v_addr, do_addr + dos * Cfg::kTileBytes, smem_u32(sDltCol) + dos * Cfg::kColPanel);
+                umma_commit_pred(leader, &dp_full[dos]);
+                GQA_TRACE(1, gi, 3);
+            }
         }
     } else if (warp == Cfg::kWarpMmaDV) {
         // ======================= issuer: dV += P^T dO(it)  (A from TMEM, B = dO read MN-major) =======================
         const uint32_t leader = elect_one() ? 1u : 0u;
         const uint32_t idesc = make_idesc_bf16(128, D, false, true);
+        int gi = 0;
         bool ok = true;
-        for (int it = 0; it < n_iter && ok; ++it) {
-            const int dos = it % Cfg::kDOStages;
-            ok = mbar_wait(&do_full[dos], (it / Cfg::kDOStages) & 1, ctx, 30) && mbar_wait(p_ready, it & 1, ctx, 31);
-            if (!ok) break;
-            tc_fence_after_sync();
-            GQA_TRACE(3, it, 0);
-            const uint32_t b0 = do_addr + dos * Cfg::kTileBytes;
+        for (int j = 0; ok; ++j) {
+            const int idx = fetch_item(j);
+            if (idx < 0) break;
+            const int n_iter = decode(idx).n_iter;
+            if (j > 0) ok = mbar_wait(acc_empty, (j - 1) & 1, ctx, 37);  // the epilogue has read the previous item's dV
+            for (int it = 0; it < n_iter && ok; ++it, ++gi) {
+                const int dos = gi % Cfg::kDOStages;
+                ok = mbar_wait(&do_full[dos], (gi / Cfg::kDOStages) & 1, ctx, 30) && mbar_wait(p_ready, gi & 1, ctx, 31);
+                if (!ok) break;
+                tc_fence_after_sync();
+                GQA_TRACE(3, gi, 0);
+                const uint32_t b0 = do_addr + dos * Cfg::kTileBytes;
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-                umma_ts_pred(leader, tmem + Cfg::kColDV, tmem + p_col_of_kstep<D>(kk),
-                             make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
-            umma_commit_pred(leader, &p_free[dos]);
-            GQA_TRACE(3, it, 1);
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_ts_pred(leader, tmem + Cfg::kColDV, tmem + p_col_of_kstep<D>(kk),
+                                 make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+                umma_commit_pred(leader, &p_free[dos]);
+                GQA_TRACE(3, gi, 1);
+            }
+            if (ok) umma_commit_pred(leader, acc_full);
         }
-        if (ok) umma_commit_pred(leader, acc_full);
     } else if (warp == Cfg::kWarpMmaDK) {
         // ======================= issuer: dK += dS^T Q(it)  (A = dS^T K-major, B = Q read MN-major), then dQ(it) =======================
         const uint32_t leader = elect_one() ? 1u : 0u;
         const uint32_t idesc = make_idesc_bf16(128, D, false, true);
-        bool ok = mbar_wait(kv_full, 0, ctx, 34);
-        for (int it = 0; it < n_iter && ok; ++it) {
-            const int qs = it % Cfg::kQStages;
-            ok = mbar_wait(&q_full[qs], (it / Cfg::kQStages) & 1, ctx, 32) && mbar_wait(ds_ready, it & 1, ctx, 33);
-            if (!ok) break;
-            tc_fence_after_sync();
-            GQA_TRACE(4, it, 0);
-            const uint32_t b0 = q_addr + qs * Cfg::kTileBytes;
-            const uint32_t ds_buf = ds_addr;
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-                if constexpr (Cfg::kDsInTmem)  // A = bf16 dS^T in the dP^T columns: query columns [16kk, 16kk+16)
-                    umma_ts_pred(leader, tmem + Cfg::kColDK, tmem + Cfg::kColDP + (kk / Cfg::kHalves) * Cfg::kCols + (kk % Cfg::kHalves) * 8,
-                                 make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
-                else
-                    umma_ss_pred(leader, tmem + Cfg::kColDK,
-                                 make_sdesc_sw128(ds_buf + (kk >> 2) * kPanel + (kk & 3) * 32, 16, 1024),
-                                 make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
-            }
-            umma_commit_pred(leader, &dk_done[qs]);
-            GQA_TRACE(4, it, 1);
-            if constexpr (!kWithDQ) {
-                umma_commit_pred(leader, ds_free);  // dK(it) was the last reader of dS^T(it)
-            } else {  // dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major)
-                if (it > 0) ok = mbar_wait(dq_empty, (it - 1) & 1, ctx, 36);
+        int gi = 0;
+        bool ok = true;
+        for (int j = 0; ok; ++j) {
+            const int idx = fetch_item(j);
+            if (idx < 0) break;
+            const int n_iter = decode(idx).n_iter;
+            ok = mbar_wait(kv_full, j & 1, ctx, 34);
+            if (ok && j > 0) ok = mbar_wait(acc_empty, (j - 1) & 1, ctx, 38);  // the epilogue has read the previous item's dK
+            for (int it = 0; it < n_iter && ok; ++it, ++gi) {
+                const int qs = gi % Cfg::kQStages;
+                ok = mbar_wait(&q_full[qs], (gi / Cfg::kQStages) & 1, ctx, 32) && mbar_wait(ds_ready, gi & 1, ctx, 33);
                 if (!ok) break;
                 tc_fence_after_sync();
-                GQA_TRACE(4, it, 2);
-                const uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);
+                GQA_TRACE(4, gi, 0);
+                const uint32_t b0 = q_addr + qs * Cfg::kTileBytes;
+                const uint32_t ds_buf = ds_addr;
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    umma_ss_pred(leader, tmem + Cfg::kColDQ, make_sdesc_sw128(ds_buf + kk * 2048, kPanel, 1024),
-                                 make_sdesc_sw128(k_addr + kk * 2048, kPanel, 1024), idesc_dq, kk > 0);
-                umma_commit_pred(leader, ds_free);
-                GQA_TRACE(4, it, 3);
+                for (int kk = 0; kk < 8; ++kk) {
+                    if constexpr (Cfg::kDsInTmem)  // A = bf16 dS^T in the dP^T columns: query columns [16kk, 16kk+16)
+                        umma_ts_pred(leader, tmem + Cfg::kColDK, tmem + Cfg::kColDP + (kk / Cfg::kHalves) * Cfg::kCols + (kk % Cfg::kHalves) * 8,
+                                     make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+                    else
+                        umma_ss_pred(leader, tmem + Cfg::kColDK,
+                                     make_sdesc_sw128(ds_buf + (kk >> 2) * kPanel + (kk & 3) * 32, 16, 1024),
+                                     make_sdesc_sw128(b0 + kk * 2048, kPanel, 1024), idesc, (it > 0 || kk > 0));
+                }
+                umma_commit_pred(leader, &dk_done[qs]);
+                GQA_TRACE(4, gi, 1);
+                if constexpr (!kWithDQ) {
+                    umma_commit_pred(leader, ds_free);  // dK(it) was the last reader of dS^T(it)
+                } else {  // dQ(it) = dS K  (A = dS^T read MN-major, B = K read MN-major)
+                    if (gi > 0) ok = mbar_wait(dq_empty, (gi - 1) & 1, ctx, 36);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    GQA_TRACE(4, gi, 2);
+                    const uint32_t idesc_dq = make_idesc_bf16(128, D, true, true);
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        umma_ss_pred(leader, tmem + Cfg::kColDQ, make_sdesc_sw128(ds_buf + kk * 2048, kPanel, 1024),
+                                     make_sdesc_sw128(k_addr + kk * 2048, kPanel, 1024), idesc_dq, kk > 0);
+                    umma_commit_pred(leader, ds_free);
+                    GQA_TRACE(4, gi, 3);
+                }
+            }
+            if (ok) {
+                umma_commit_pred(leader, acc_full);
+                umma_commit_pred(leader, kv_empty);  // every product of the item that reads K (dQ) or V (dP^T, ordered before
+                                                     // dK by ds_ready) has finished when this fires
             }
         }
-        if (ok) umma_commit_pred(leader, acc_full);
     } else if (warp < kWarpEw0) {
         if constexpr (kWithDQ) {
         // ======================= dQ drain warps =======================
@@ -434,11 +578,15 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         constexpr int kWarpStage = Cfg::kDqBoxes * 4096;
         uint8_t* stage = sDQ + warp * kWarpStage + lane * 128;
         const int sw = lane & 7;
+        // The loop exists twice, with and without the deterministic mode's bookkeeping (the `det` tag below): the role
+        // is short of registers, and the default path should not carry the turn state.
+        auto drain_items = [&](auto det) {
+        constexpr bool kDet = decltype(det)::value;
         // Deterministic mode: the reductions into one 32-row slice of the accumulator are applied in KV-tile order.
         // The CTA of KV tile kt waits until the slice's counter reads kt (its predecessors run or have run: they
         // have smaller block indices), and hands on with kt + 1 once its own reductions have completed.
         // Fill cost: CTA kt starts its first reduction kt hand-overs late; after that the stagger persists.
-        auto turn_acquire = [&](unsigned int* turn, unsigned int early) -> bool {
+        auto turn_acquire = [&](unsigned int* turn, unsigned int early, int kt) -> bool {
             uint32_t good = 1;
             if (lane == 0) {
                 const long long t0 = clock64();
@@ -463,25 +611,43 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // completion is short.  (Holding the turns of three tiles instead was slower: the hand-over delay, not the
         // wait, is what the CTAs of a group queue on.)
         unsigned int* held = nullptr;  // slice whose turn this warp still holds
+        unsigned int held_next = 0;    // the value that hands it on: 1 + the KV tile it was taken for
         auto release_held = [&]() {
-            if (held) {
+            if (kDet && held) {
                 if (lane == 0) {
                     bulk_wait_all();  // completed: the sums are visible to this thread
-                    st_release_gpu(held, (unsigned)kt + 1u);
+                    st_release_gpu(held, held_next);
                 }
                 __syncwarp();
                 held = nullptr;
             }
         };
-        for (int it = 0; it < n_iter; ++it) {
-            const int row = q_y_of(it) + warp * 32, wz = ws_z_of(it);  // first query position of this warp's slice
-            unsigned int* turn = p.dq_turn ? p.dq_turn + ((size_t)wz * p.n_tiles + row / kTile) * 4 + warp : nullptr;
-            bool turn_mine = (turn == nullptr);  // becomes true once this warp may reduce into the slice
+        int gi = 0;
+        bool going = true;
+        for (int j = 0; going; ++j) {
+        // per item only what the loop needs, kept as running coordinates (registers are short in this role)
+        int kt, n_left, n_qt, row0, row, wz;
+        {
+            const int idx = fetch_item(j);
+            if (idx < 0) break;
+            const WorkItem w = decode(idx);
+            kt = w.kt;
+            n_left = w.n_iter;
+            n_qt = w.n_qt;
+            row0 = w.qt0 * kTile + warp * 32;  // first query position of this warp's slice in the item's lowest tile
+            row = q_y_of(w, 0) + warp * 32;    // ... and in the tile its loop starts with
+            wz = ws_z_of(w, 0);
+        }
+        const int row_end = row0 + n_qt * kTile;
+        int qi = 0;  // tiles done in the current query head
+        for (; n_left > 0; --n_left, ++gi) {
+            unsigned int* turn = kDet ? p.dq_turn + ((size_t)wz * p.n_tiles + row / kTile) * 4 + warp : nullptr;
+            bool turn_mine = !kDet;  // becomes true once this warp may reduce into the slice
             // first look at the counter now: its round trip to L2 hides behind the TMEM loads and the staging
-            const unsigned int early = (turn && lane == 0) ? ld_acquire_gpu(turn) : 0xffffffffu;
-            if (!mbar_wait(ds_free, it & 1, ctx, 40)) break;  // dQ(it) complete
+            const unsigned int early = (kDet && lane == 0) ? ld_acquire_gpu(turn) : 0xffffffffu;
+            if (!mbar_wait(ds_free, gi & 1, ctx, 40)) { going = false; break; }  // dQ(it) complete
             tc_fence_after_sync();
-            GQA_TRACE(2, it, 0);
+            GQA_TRACE(2, gi, 0);
             constexpr int kRounds = D / (32 * Cfg::kDqBoxes);
             if constexpr (Cfg::kDrainEarlyRelease) {
                 static_assert(!Cfg::kDrainEarlyRelease || (D == 128 && Cfg::kDqBoxes == 1), "four 32-column chunks, one box");
@@ -512,7 +678,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 tc_fence_before_sync();
                 mbar_arrive(dq_empty);     // the dP^T columns are free after two TMEM round trips
                 release_held();
-                if (!turn_mine) turn_mine = turn_acquire(turn, early);
+                if (kDet && !turn_mine) turn_mine = turn_acquire(turn, early, kt);
                 reduce_box(0);
                 stage_box(vb);
                 reduce_box(1);
@@ -520,10 +686,12 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 reduce_box(2);
                 stage_box(va);
                 reduce_box(3);
-                if (turn && turn_mine) held = turn;
+                if (kDet && turn_mine) { held = turn; held_next = (unsigned)kt + 1u; }
             } else {
     #pragma unroll 1
                 for (int rnd = 0; rnd < kRounds; ++rnd) {
+    // (unrolled on purpose: with both boxes in flight the role wants 110 registers and spills ~100 bytes under the
+    // kernel's 80, but the rolled loop, which fits, makes the drain the slowest role: measured 10 % slower)
     #pragma unroll
                     for (int bx = 0; bx < Cfg::kDqBoxes; ++bx) {
                         uint32_t v[32];
@@ -541,9 +709,9 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     fence_proxy_async_smem();
                     __syncwarp();
                     release_held();
-                    GQA_TRACE(2, it, 2);
-                    if (!turn_mine) turn_mine = turn_acquire(turn, early);
-                    GQA_TRACE(2, it, 3);
+                    GQA_TRACE(2, gi, 2);
+                    if (kDet && !turn_mine) turn_mine = turn_acquire(turn, early, kt);
+                    GQA_TRACE(2, gi, 3);
                     if (turn_mine && lane == 0) {
     #pragma unroll
                         for (int bx = 0; bx < Cfg::kDqBoxes; ++bx)
@@ -553,13 +721,25 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     }
                     __syncwarp();
                 }
-                if (turn && turn_mine) held = turn;
+                if (kDet && turn_mine) { held = turn; held_next = (unsigned)kt + 1u; }
             }
-            if (!turn_mine) break;  // a bounded wait gave up: the abort flag is set
-            GQA_TRACE(2, it, 1);
+            if (!turn_mine) { going = false; break; }  // a bounded wait gave up: the abort flag is set
+            GQA_TRACE(2, gi, 1);
+            row += kTile;  // next tile of the head (the loop wraps around at the head's last tile) ...
+            if (row == row_end) row = row0;
+            if (++qi == n_qt) {  // ... or the same start tile of the next head
+                qi = 0;
+                ++wz;
+            }
+        }
         }
         if (warp == 0) GQA_MARK(7);
         release_held();
+        };
+        if (p.dq_turn)
+            drain_items(std::true_type{});
+        else
+            drain_items(std::false_type{});
         if (lane == 0) bulk_wait_all();
         if (warp == 0) GQA_MARK(8);
         }
@@ -645,95 +825,51 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             mbar_arrive(p_ready);
         };
 
-        // ---- prologue: P^T(0)
-        ok = mbar_wait(&s_full[0], 0, ctx, 51);
-        if (trace_me) GQA_MARK(2);
-        if (ok) {
+        // S^T(g) -> P^T(g), published for dV
+        auto make_p = [&](int g, bool masked) -> bool {
+            if (!mbar_wait(&s_full[g % Cfg::kQStages], (g / Cfg::kQStages) & 1, ctx, 51)) return false;
             tc_fence_after_sync();
-            const bool masked0 = p.causal != 0;  // iteration 0 is the diagonal tile when causal
-#pragma unroll
-            for (int hf = 0; hf < H; ++hf) {
-                uint32_t v[16];
-                tmem_ld16(tS + hf * 16, v);
-                tmem_wait_ld();
-                p_half(v, hf, masked0, pk_cur + hf * 8);
-            }
-            publish_p(pk_cur);
-        }
-        for (int it = 0; it < n_iter && ok; ++it) {
-            const bool more = it + 1 < n_iter;
-            const bool masked_next = p.causal && ((it + 1) % n_qt == 0);
-            // ---- dS^T(it) from dP^T(it) and the P^T(it) kept in registers
-            ok = mbar_wait(&dp_full[it % Cfg::kDOStages], (it / Cfg::kDOStages) & 1, ctx, 53);
-            if (ok && it > 0) ok = mbar_wait(ds_free, (it - 1) & 1, ctx, 54);  // dK(it-1) and dQ(it-1) have read dS^T(it-1)
-            if (!ok) break;
-            tc_fence_after_sync();
-            if (trace_me) GQA_TRACE(0, it, 0);
-            {
-                uint32_t dsp[C / 2];
-#pragma unroll
-                for (int hf = 0; hf < H; ++hf) {
-                    uint32_t vd[16];
-                    tmem_ld16(tDP + hf * 16, vd);
-                    tmem_wait_ld();
-                    ds_half(vd, hf, pk_cur + hf * 8, dsp + hf * 8, ds_row0);
-                }
-                if constexpr (Cfg::kDsInTmem) {
-                    static_assert(!Cfg::kDsInTmem || C == 32, "the TMEM copy of dS^T is written as one 16-column store");
-                    uint32_t t16[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) t16[i] = dsp[i];
-                    tmem_st16(tDP, t16);  // over this thread's own, already consumed, dP^T columns
-                    tmem_wait_st();
-                }
-            }
-            if constexpr (kWithDQ || !Cfg::kDsInTmem) fence_proxy_async_smem();
-            tc_fence_before_sync();
-            mbar_arrive(ds_ready);
-            if (trace_me) GQA_TRACE(0, it, 1);
-            if (!more) break;
-            // ---- P^T(it+1) from S^T(it+1)
-            ok = mbar_wait(&s_full[(it + 1) % Cfg::kQStages], ((it + 1) / Cfg::kQStages) & 1, ctx, 51);
-            if (!ok) break;
-            tc_fence_after_sync();
-            if (trace_me) GQA_TRACE(0, it, 2);
+            if (trace_me) GQA_TRACE(0, g - 1, 2);
 #pragma unroll
             for (int hf = 0; hf < H; ++hf) {
                 uint32_t vs[16];
                 tmem_ld16(tS + hf * 16, vs);
                 tmem_wait_ld();
-                p_half(vs, hf, masked_next, pk_cur + hf * 8);
+                p_half(vs, hf, masked, pk_cur + hf * 8);
             }
             if constexpr (!Cfg::kPAliasesS) {
-                // dV(it) has consumed P^T(it): its columns can be rewritten
-                ok = mbar_wait(&p_free[it % Cfg::kDOStages], (it / Cfg::kDOStages) & 1, ctx, 52);
-                if (!ok) break;
-                tc_fence_after_sync();
+                if (g > 0) {  // dV(g-1) has consumed P^T(g-1): its columns can be rewritten
+                    if (!mbar_wait(&p_free[(g - 1) % Cfg::kDOStages], ((g - 1) / Cfg::kDOStages) & 1, ctx, 52)) return false;
+                    tc_fence_after_sync();
+                }
             }
             publish_p(pk_cur);
-            if (trace_me) GQA_TRACE(0, it, 3);
-        }
-        // ---- epilogue: dV and scale*dK of this key row, a quarter of the columns per warpgroup ----
-        if (trace_me) GQA_MARK(4);
-        if (ok) ok = mbar_wait(acc_full, 0, ctx, 55);
-        if (trace_me) GQA_MARK(5);
-        if (ok) {
+            if (trace_me) GQA_TRACE(0, g - 1, 3);
+            return true;
+        };
+        // dV and scale*dK of this key row of work item wi (its j-th of this block), a quarter of the columns per warpgroup
+        auto epilogue = [&](int jj) -> bool {
+            // read and decoded again here (the slot is still valid): nothing of it stays live across the loop over the tile pairs
+            const WorkItem wi = decode(item_slot[jj & (kItemSlots - 1)]);
+            if (trace_me) GQA_MARK(4);
+            if (!mbar_wait(acc_full, jj & 1, ctx, 55)) return false;
+            if (trace_me) GQA_MARK(5);
             tc_fence_after_sync();
             // key rows beyond the end of the sequence are not stored (the TMEM loads below are warp-wide
             // instructions: every lane runs them, only the stores are guarded)
-            const bool row_ok = kt * kTile + j < p.S;
+            const bool row_ok = wi.kt * kTile + j < p.S;
             constexpr int kQuarter = D / Cfg::kEwGroups;  // columns of dV / dK per warpgroup
             // element offset of this key row in dK / dV
-            const size_t kv_pos = (size_t)kt * kTile + j;
-            const size_t kv_elem = p.bshd ? (((size_t)b * p.S + kv_pos) * p.Hkv + hkv) * D
-                                          : (((size_t)b * p.Hkv + hkv) * p.S + kv_pos) * p.d_real;
+            const size_t kv_pos = (size_t)wi.kt * kTile + j;
+            const size_t kv_elem = p.bshd ? (((size_t)wi.b * p.S + kv_pos) * p.Hkv + wi.hkv) * D
+                                          : (((size_t)wi.b * p.Hkv + wi.hkv) * p.S + kv_pos) * p.d_real;
 #pragma unroll 1
             for (int which = 0; which < 2; ++which) {
                 const uint32_t tA = tmem + lane_addr + (which == 0 ? Cfg::kColDV : Cfg::kColDK) + w * kQuarter;
                 __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + kv_elem + w * kQuarter;
                 // head split: fp32 sums of this part, [part][which][key row in [B,Hkv,S] order][D]
-                float* pdst = p.parts > 1 ? p.partial + (((size_t)(part * 2 + which) * ((size_t)groups * p.S)) +
-                                                         (size_t)grp * p.S + kv_pos) * D + w * kQuarter
+                float* pdst = p.parts > 1 ? p.partial + (((size_t)(wi.part * 2 + which) * ((size_t)p.groups * p.S)) +
+                                                         (size_t)wi.grp * p.S + kv_pos) * D + w * kQuarter
                                           : nullptr;
                 const float mul = which == 0 ? 1.0f : p.scale;
 #pragma unroll
@@ -761,6 +897,62 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     }
                 }
             }
+            // every accumulator value is in registers or on its way to memory: the next item's products may overwrite them
+            tc_fence_before_sync();
+            mbar_arrive(acc_empty);
+            return true;
+        };
+
+        int gi = 0;  // iteration index over all items of this block
+        for (int jj = 0; ok; ++jj) {
+            int n_iter, n_qt;
+            {
+                const int idx = fetch_item(jj);
+                if (idx < 0) break;
+                const WorkItem wi = decode(idx);
+                n_iter = wi.n_iter;
+                n_qt = wi.n_qt;
+                if (warp == kWarpEw0 && lane == 0) GQA_ITEM_BEGIN(idx);
+            }
+            // ---- prologue: P^T of the item's first iteration (the diagonal tile when causal)
+            ok = make_p(gi, p.causal != 0);
+            if (trace_me) GQA_MARK(2);
+            for (int it = 0; it < n_iter && ok; ++it, ++gi) {
+                // ---- dS^T(it) from dP^T(it) and the P^T(it) kept in registers
+                ok = mbar_wait(&dp_full[gi % Cfg::kDOStages], (gi / Cfg::kDOStages) & 1, ctx, 53);
+                if (ok && gi > 0) ok = mbar_wait(ds_free, (gi - 1) & 1, ctx, 54);  // dK and dQ of the iteration before have read its dS^T
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (trace_me) GQA_TRACE(0, gi, 0);
+                {
+                    uint32_t dsp[C / 2];
+#pragma unroll
+                    for (int hf = 0; hf < H; ++hf) {
+                        uint32_t vd[16];
+                        tmem_ld16(tDP + hf * 16, vd);
+                        tmem_wait_ld();
+                        ds_half(vd, hf, pk_cur + hf * 8, dsp + hf * 8, ds_row0);
+                    }
+                    if constexpr (Cfg::kDsInTmem) {
+                        static_assert(!Cfg::kDsInTmem || C == 32, "the TMEM copy of dS^T is written as one 16-column store");
+                        uint32_t t16[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) t16[i] = dsp[i];
+                        tmem_st16(tDP, t16);  // over this thread's own, already consumed, dP^T columns
+                        tmem_wait_st();
+                    }
+                }
+                if constexpr (kWithDQ || !Cfg::kDsInTmem) fence_proxy_async_smem();
+                tc_fence_before_sync();
+                mbar_arrive(ds_ready);
+                if (trace_me) GQA_TRACE(0, gi, 1);
+                if (it + 1 == n_iter) continue;
+                // ---- P^T(it+1) from S^T(it+1)
+                ok = make_p(gi + 1, p.causal && ((it + 1) % n_qt == 0));
+            }
+            // ---- epilogue, before the next item's first P^T: the issuers need the accumulators back for its products
+            if (ok) ok = epilogue(jj);
+            if (warp == kWarpEw0 && lane == 0) GQA_ITEM_END(item_slot[jj & (kItemSlots - 1)]);
         }
     }
 
@@ -773,6 +965,34 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (*abort_flag != 0) abort_grace_period();  // in-flight copies and MMAs land before TMEM is released
         tmem_dealloc(tmem, Cfg::kTmemCols);
     }
+}
+
+// Thread blocks of the main kernel that run at the same time: one per SM (shared memory and TMEM allow no second).
+int resident_blocks() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+    if (dev != cached_dev) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) return 1;
+        cached = sms;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+// Causal order: how many (batch, KV head) groups form a super-group (the list runs super-group by super-group, KV
+// tile by KV tile inside, longest items first).  Few groups at a time means many KV tiles of the same group in
+// flight together, all streaming that group's Q/dO tiles through L2 at nearly the same time, so HBM is read fewer
+// times (measured: 7 % at B4 Hq32 Hkv8 S8192 D128, 3 % at the headline shape with a causal mask, 2 % at S = 32768).
+// The bound keeps the end of the launch balanced: a super-group must last about as long as its longest item
+// (n_tiles tile pairs per head against sg * n_tiles * (n_tiles + 1) / 2 spread over the SMs), or the long items of
+// the last super-group would start too late for the others to level them out.
+int causal_super_group(int groups, int n_tiles, int sms) {
+    const int bound = (2 * sms + n_tiles) / (n_tiles + 1);  // ceil(2 * sms / (n_tiles + 1))
+    for (int d = 1; d <= groups; ++d)
+        if (groups % d == 0 && d >= bound) return d;
+    return groups;
 }
 
 // dq_accum == nullptr selects the variant without the dQ part.
@@ -825,7 +1045,11 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.G = s.G();
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
-    const unsigned grid = (unsigned)(p.n_tiles * s.B * s.Hkv * parts);
+    p.groups = s.B * s.Hkv;
+    p.sg = dq_turn ? p.groups : causal_super_group(p.groups, p.n_tiles, resident_blocks());
+    p.n_items = p.n_tiles * p.groups * parts;
+    // persistent, except in the deterministic mode (see the work-item comment in the kernel)
+    const unsigned grid = (unsigned)(dq_turn ? p.n_items : std::min(p.n_items, resident_blocks()));
     kernel<<<grid, Cfg::kThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, mdo, mdq, mlse, mdlt, p);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());
@@ -837,6 +1061,9 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
 #ifdef GQA_BWD_TRACE
 extern "C" int gqa_debug_copy_bwd_trace(long long* host) {
     return (int)cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(g_bwd_trace));
+}
+extern "C" int gqa_debug_copy_bwd_items(long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, g_bwd_items, sizeof(g_bwd_items));
 }
 extern "C" int gqa_debug_copy_bwd_marks(long long* host) {
     return (int)cudaMemcpyFromSymbol(host, g_bwd_marks, sizeof(g_bwd_marks));

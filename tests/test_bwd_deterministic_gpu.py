@@ -38,7 +38,8 @@ def test_deterministic_backward_matches_oracle(gqa_lib, oracle, shape, causal):
 @pytest.mark.parametrize("shape", [(2, 12, 4, 2048, 64), (2, 8, 2, 2048, 128), (8, 12, 4, 4096, 64)])
 def test_deterministic_backward_is_bit_reproducible(gqa_lib, shape, causal):
     """More thread blocks than SMs, several per (batch, KV head) group: every dQ tile gets up to S/128 ordered
-    reductions.  Four runs, all three gradients bit-identical; the default mode agrees up to fp32 rounding."""
+    reductions.  Four runs, all three gradients bit-identical; the default mode agrees up to the order of its fp32
+    sums."""
     B, Hq, Hkv, S, D = shape
     gen = torch.Generator(device="cuda").manual_seed(5)
     q = torch.randn(B, Hq, S, D, generator=gen, device="cuda").bfloat16()
@@ -56,7 +57,14 @@ def test_deterministic_backward_is_bit_reproducible(gqa_lib, shape, causal):
         assert torch.equal(dk, runs[0][1]) and torch.equal(dv, runs[0][2])
     dq0, dk0, dv0 = ops.gqa_backward(q, k, v, o, do, lse, causal=causal, workspace=ws)
     ops.check_status(ws)
-    assert torch.equal(dk0, runs[0][1]) and torch.equal(dv0, runs[0][2])
+    if causal:
+        assert torch.equal(dk0, runs[0][1]) and torch.equal(dv0, runs[0][2])
+    else:
+        # without a mask the default mode starts each KV tile's loop over the query tiles at a different tile (the
+        # ordered mode does not): the same fp32 sums in another order
+        for got, want in ((dk0, runs[0][1]), (dv0, runs[0][2])):
+            m = util.metrics(util.to_np(got), util.to_np(want))
+            assert m["rel_rms"] < 2e-3, m
     m = util.metrics(util.to_np(dq0), util.to_np(runs[0][0]))
     assert m["rel_rms"] < 2e-3, m
 

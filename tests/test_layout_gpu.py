@@ -35,9 +35,16 @@ def test_bshd_forward_and_backward_equal_bhsd(gqa_lib, shape, causal):
     assert dq2.shape == (B, S, Hq, D) and dk2.shape == (B, S, Hkv, D)
     assert torch.equal(_t(dk), dk2) and torch.equal(_t(dv), dv2)
     assert torch.equal(_t(dq), dq2)
+    # default mode: dK, dV again bit for bit between the layouts (against the ordered mode they may differ in the
+    # order of the fp32 sums: without a mask the default mode starts its loops at other query tiles)
+    _, dk0, dv0 = ops.gqa_backward(q, k, v, o, do, lse, causal=causal, workspace=ws)
+    ops.check_status(ws)
     dq3, dk3, dv3 = ops.gqa_backward(_t(q), _t(k), _t(v), o2, _t(do), lse2, causal=causal, workspace=ws, layout="bshd")
     ops.check_status(ws)
-    assert torch.equal(dk3, dk2) and torch.equal(dv3, dv2)
+    assert torch.equal(dk3, _t(dk0)) and torch.equal(dv3, _t(dv0))
+    for got, want in ((dk3, dk2), (dv3, dv2)):
+        m = util.metrics(util.to_np(got), util.to_np(want))
+        assert m["rel_rms"] < 2e-3, m
     m = util.metrics(util.to_np(dq3), util.to_np(dq2))
     assert m["rel_rms"] < 2e-3, m
 
