@@ -8,12 +8,16 @@ raises if the library or a CUDA device is missing.
 """
 from .capi import GqaError, lib_path, load_library  # noqa: F401
 from .ops import (  # noqa: F401
+    bwd_varlen_workspace_bytes,
     bwd_workspace_bytes,
     gqa_backward,
+    gqa_backward_varlen,
     gqa_delta,
     gqa_forward,
+    gqa_forward_varlen,
     launch_count,
 )
 
 __all__ = ["GqaError", "lib_path", "load_library", "gqa_forward", "gqa_backward", "gqa_delta",
-           "bwd_workspace_bytes", "launch_count"]
+           "bwd_workspace_bytes", "launch_count", "gqa_forward_varlen", "gqa_backward_varlen",
+           "bwd_varlen_workspace_bytes"]

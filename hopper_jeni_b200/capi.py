@@ -35,6 +35,10 @@ EXPORTS = {
     "gqa_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "gqa_bwd_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp,
                         ctypes.c_uint]),
+    "gqa_fwd_varlen": (_i, [_vp, _vp, _vp, _vp, _fp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "gqa_bwd_varlen_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "gqa_bwd_varlen": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
+                            _vp]),
     "gqa_bwd_static_scratch_bytes": (_sz, []),
     "gqa_bwd_static_scratch": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "gqa_bwd_stage_times": (_i, [_vp, _vp, _vp, _vp, _vp, _fp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,

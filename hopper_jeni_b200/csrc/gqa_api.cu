@@ -38,8 +38,23 @@ int check_shape(int B, int Hq, int Hkv, int S, int D) {
 
 namespace {
 
+// A packed variable-length batch as the kernels see it: one [total, H*D] matrix per tensor (B = 1, S = total,
+// sequence-major) plus the sequence starts.  Only the two head dimensions with native kernels.
+struct Packed {
+    const int* cu_seqlens;
+    int n_seqs, max_seqlen;
+};
+
+int check_packed(const int* cu_seqlens, int n_seqs, int total_tokens, int max_seqlen, int D) {
+    if (!cu_seqlens || n_seqs <= 0 || total_tokens <= 0 || max_seqlen <= 0 || max_seqlen > total_tokens)
+        return GQA_ERR_BAD_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(cu_seqlens) & 3u) return GQA_ERR_BAD_ARGUMENT;
+    if (D != 64 && D != 128) return GQA_ERR_UNSUPPORTED;
+    return GQA_OK;
+}
+
 int run_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv, int S, int D,
-            int causal, float scale, cudaStream_t stream, unsigned int flags) {
+            int causal, float scale, cudaStream_t stream, unsigned int flags, const Packed* packed = nullptr) {
     if (flags & ~(unsigned)GQA_LAYOUT_BSHD) return GQA_ERR_BAD_ARGUMENT;
     if (!Q || !K || !V || !O || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
@@ -56,6 +71,11 @@ int run_fwd(const void* Q, const void* K, const void* V, void* O, float* LSE, in
     if (rc) return rc;
     Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
     s.bshd = (flags & GQA_LAYOUT_BSHD) ? 1 : 0;
+    if (packed) {
+        s.cu_seqlens = packed->cu_seqlens;
+        s.n_seqs = packed->n_seqs;
+        s.max_seqlen = packed->max_seqlen;
+    }
     return gqa::launch_fwd_sm100(Q, K, V, O, LSE, s, status, stream);
 }
 
@@ -74,6 +94,21 @@ extern "C" int gqa_fwd_ex(const void* Q, const void* K, const void* V, void* O, 
 extern "C" int launch_gqa(const void* Q, const void* K, const void* V, void* O, float* LSE, int B, int Hq, int Hkv,
                           int S, int D, int causal, float scale, gqa_stream_t stream) {
     return gqa_fwd(Q, K, V, O, LSE, B, Hq, Hkv, S, D, causal, scale, stream);
+}
+
+extern "C" int gqa_fwd_varlen(const void* Q, const void* K, const void* V, void* O, float* LSE, const int* cu_seqlens,
+                              int n_seqs, int total_tokens, int max_seqlen, int Hq, int Hkv, int D, int causal,
+                              float scale, gqa_stream_t stream) {
+    const int rc = check_packed(cu_seqlens, n_seqs, total_tokens, max_seqlen, D);
+    if (rc) return rc;
+    const Packed packed{cu_seqlens, n_seqs, max_seqlen};
+    return run_fwd(Q, K, V, O, LSE, 1, Hq, Hkv, total_tokens, D, causal, scale, reinterpret_cast<cudaStream_t>(stream),
+                   GQA_LAYOUT_BSHD, &packed);
+}
+
+extern "C" size_t gqa_bwd_varlen_workspace_bytes(int total_tokens, int Hq, int Hkv, int D) {
+    if (D != 64 && D != 128) return 0;
+    return gqa_bwd_workspace_bytes(1, Hq, Hkv, total_tokens, D, 0);
 }
 
 extern "C" size_t gqa_bwd_workspace_bytes(int B, int Hq, int Hkv, int S, int D, int causal) {
@@ -97,9 +132,11 @@ namespace {
 // Shared body of gqa_bwd and gqa_bwd_stage_times; `ev` is null or four events recorded around the stages.
 int run_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* LSE, void* dQ,
             void* dK, void* dV, int B, int Hq, int Hkv, int S, int D, int causal, float scale, void* workspace,
-            size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev, unsigned int flags = 0) {
+            size_t workspace_bytes, cudaStream_t stream, cudaEvent_t* ev, unsigned int flags = 0,
+            const Packed* packed = nullptr) {
     if (flags & ~(unsigned)(GQA_BWD_DETERMINISTIC | GQA_LAYOUT_BSHD | GQA_BWD_SPLIT_HEADS | GQA_BWD_DQ_SEPARATE))
         return GQA_ERR_BAD_ARGUMENT;
+    if (packed && flags != GQA_LAYOUT_BSHD) return GQA_ERR_BAD_ARGUMENT;  // no ordered mode, head split or separate dQ pass
     if (!Q || !K || !V || !O || !dO || !LSE || !dQ || !dK || !dV || !scale_ok(scale)) return GQA_ERR_BAD_ARGUMENT;
     int rc = check_shape(B, Hq, Hkv, S, D);
     if (rc) return rc;
@@ -109,6 +146,11 @@ int run_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
         if (!gqa::aligned16(p)) return GQA_ERR_BAD_ARGUMENT;
     Shape s{B, Hq, Hkv, S, D, causal ? 1 : 0, scale};
     s.bshd = (flags & GQA_LAYOUT_BSHD) ? 1 : 0;
+    if (packed) {
+        s.cu_seqlens = packed->cu_seqlens;
+        s.n_seqs = packed->n_seqs;
+        s.max_seqlen = packed->max_seqlen;
+    }
     const int parts = (flags & GQA_BWD_SPLIT_HEADS) ? gqa::bwd_head_parts(s) : 1;
     const gqa::BwdWorkspace ws(s, parts);
     if (!workspace || workspace_bytes < ws.total) {
@@ -173,6 +215,17 @@ extern "C" int gqa_bwd_ex(const void* Q, const void* K, const void* V, const voi
                           void* workspace, size_t workspace_bytes, gqa_stream_t stream, unsigned int flags) {
     return run_bwd(Q, K, V, O, dO, LSE, dQ, dK, dV, B, Hq, Hkv, S, D, causal, scale, workspace, workspace_bytes,
                    reinterpret_cast<cudaStream_t>(stream), nullptr, flags);
+}
+
+extern "C" int gqa_bwd_varlen(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                              const float* LSE, void* dQ, void* dK, void* dV, const int* cu_seqlens, int n_seqs,
+                              int total_tokens, int max_seqlen, int Hq, int Hkv, int D, int causal, float scale,
+                              void* workspace, size_t workspace_bytes, gqa_stream_t stream) {
+    const int rc = check_packed(cu_seqlens, n_seqs, total_tokens, max_seqlen, D);
+    if (rc) return rc;
+    const Packed packed{cu_seqlens, n_seqs, max_seqlen};
+    return run_bwd(Q, K, V, O, dO, LSE, dQ, dK, dV, 1, Hq, Hkv, total_tokens, D, causal, scale, workspace,
+                   workspace_bytes, reinterpret_cast<cudaStream_t>(stream), nullptr, GQA_LAYOUT_BSHD, &packed);
 }
 
 extern "C" int gqa_bwd_stage_times(const void* Q, const void* K, const void* V, const void* O, const void* dO,

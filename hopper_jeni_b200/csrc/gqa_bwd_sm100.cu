@@ -175,6 +175,7 @@ struct BwdParams {
     float* partial;
     int parts;
     int groups;   // B * Hkv
+    const int* cu;  // packed variable-length batch: sequence starts (n_seqs + 1), else null
     int sg;       // causal order: (batch, KV head) groups per super-group (see the work-item comment)
     int n_items;  // n_tiles * groups * parts: work items, each handled by one thread block at a time
     int Hq, Hkv, S, causal, n_tiles, G, bshd;
@@ -191,9 +192,11 @@ __device__ __forceinline__ uint32_t p_col_of_kstep(int kk) {
     else return Cfg::kColP + kk * 8;
 }
 
+// kVarlen: packed variable-length batch (see the work-item decode): the items of the list that lie beyond their
+// sequence are skipped by the producer, the rows beyond a sequence's end are masked in P^T.
 // kWithDQ = false: the variant that leaves dQ to the separate query-parallel pass (gqa_bwd_dq_sm100.cu): no dQ
 // product, idle drain warps, and at D = 64 no dS^T in shared memory at all (dK reads its copy in TMEM).
-template <int D, bool kWithDQ>
+template <int D, bool kWithDQ, bool kVarlen>
 __global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
 gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
@@ -268,6 +271,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     struct WorkItem {
         int kt, grp, part, b, hkv, qt0, n_qt, n_iter, kv_x, kv_z;
         int shift;  // the item's loop over the query tiles of a head starts at tile qt0 + shift and wraps around
+        int y0, len;  // first row and length of the sequence in the tensors' row coordinate (0 and S unless packed)
     };
     const bool kt_major = p.causal || p.dq_turn != nullptr;
     const int g_local = p.G / p.parts;  // query heads a work item loops over
@@ -294,15 +298,28 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
         w.b = w.grp / p.Hkv;
         w.hkv = w.grp % p.Hkv;
+        w.y0 = 0;
+        w.len = p.S;
+        int n_tiles = p.n_tiles;
+        if constexpr (kVarlen) {
+            // Packed batch: "batch" w.b of the list is a sequence, a row range of the one [T, H*D] matrix (matrix
+            // index 0).  The list is laid out for max_seqlen: an item whose KV tile lies beyond its sequence comes out
+            // with n_iter <= 0 and is skipped.  Rows past the end of the sequence are another sequence's (or zeros
+            // past T): the elementwise warps zero P^T there, which zeroes dS^T and with it every contribution.
+            w.y0 = p.cu[w.b];
+            w.len = p.cu[w.b + 1] - w.y0;
+            n_tiles = (w.len + kTile - 1) / kTile;
+            w.b = 0;
+        }
         w.qt0 = p.causal ? w.kt : 0;
-        w.n_qt = p.n_tiles - w.qt0;
+        w.n_qt = n_tiles - w.qt0;
         w.n_iter = g_local * w.n_qt;
         // Non-causal: the blocks of one (batch, KV head) group start together; rotated by their KV tile index they
         // are on different query tiles at any time, so their dQ reductions do not queue on the same lines in L2 (all
         // starting at tile 0, the first waves ran 10-15 % slower per tile pair than the later, drifted-apart ones).
         // Causal blocks are staggered already (block kt starts at query tile kt); the deterministic mode wants its
         // blocks on the same tile one after the other.
-        w.shift = kt_major ? 0 : w.kt;
+        w.shift = (kt_major || kVarlen) ? 0 : w.kt;
         w.kv_x = p.bshd ? w.hkv * D : 0;
         w.kv_z = p.bshd ? w.b : w.b * p.Hkv + w.hkv;
         return w;
@@ -314,7 +331,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // K in dQ), queries beyond S give zero rows of Q, dO and of the -LSE / -Delta columns (P = 1, dS = 0).
     auto head_of = [&](const WorkItem& w, int it) { return w.hkv * p.G + w.part * g_local + it / w.n_qt; };
     auto q_y_of = [&](const WorkItem& w, int it) {  // first query position
-        return (w.qt0 + (it % w.n_qt + w.shift) % w.n_qt) * kTile;
+        return w.y0 + (w.qt0 + (it % w.n_qt + w.shift) % w.n_qt) * kTile;
     };
     auto q_x_of = [&](const WorkItem& w, int it) { return p.bshd ? head_of(w, it) * D : 0; };
     auto q_z_of = [&](const WorkItem& w, int it) { return p.bshd ? w.b : w.b * p.Hq + head_of(w, it); };
@@ -378,7 +395,18 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tma_prefetch_desc(&mapDltCol);
             unsigned int* work_counter = p.status + 16;  // zeroed with the status word before every launch
             int gi = 0;  // iterations issued so far, over all items: the rings and their barriers carry on across items
+            auto claim = [&]() -> int {  // the next unclaimed item of the list that has work, -1 when there is none
+                for (;;) {
+                    if ((int)gridDim.x >= p.n_items) return -1;
+                    const int next = (int)gridDim.x + (int)atomicAdd(work_counter, 1u);
+                    if (next >= p.n_items) return -1;
+                    if (!kVarlen || decode(next).n_iter > 0) return next;
+                }
+            };
             int idx = blockIdx.x;
+            if constexpr (kVarlen) {
+                if (decode(idx).n_iter <= 0) idx = claim();
+            }
             bool ok = true;
             for (int j = 0; ok; ++j) {
                 item_slot[j & (kItemSlots - 1)] = idx;
@@ -395,8 +423,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 }
                 mbar_expect_tx(kv_full, 2 * Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn) {
-                    tma_load_3d(sK + pn * kPanel, &mapK, kv_full, w.kv_x + pn * 64, w.kt * kTile, w.kv_z);
-                    tma_load_3d(sV + pn * kPanel, &mapV, kv_full, w.kv_x + pn * 64, w.kt * kTile, w.kv_z);
+                    tma_load_3d(sK + pn * kPanel, &mapK, kv_full, w.kv_x + pn * 64, w.y0 + w.kt * kTile, w.kv_z);
+                    tma_load_3d(sV + pn * kPanel, &mapV, kv_full, w.kv_x + pn * 64, w.y0 + w.kt * kTile, w.kv_z);
                 }
                 int next = -1;
                 for (int it = 0; it < w.n_iter; ++it, ++gi) {
@@ -406,10 +434,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                     // whole item early, the 32k-token causal shape went to HBM for them, drew 13 % more energy
                     // per tile pair and ran that much slower under the power cap); the round trip to the counter hides
                     // behind the tile pairs that are still in the rings.
-                    if (it == w.n_iter - 1 && (int)gridDim.x < p.n_items) {
-                        next = (int)gridDim.x + (int)atomicAdd(work_counter, 1u);
-                        if (next >= p.n_items) next = -1;
-                    }
+                    if (it == w.n_iter - 1) next = claim();
                     const int qx = q_x_of(w, it), qy = q_y_of(w, it), qz = q_z_of(w, it), wz = ws_z_of(w, it);
                     {
                         const int st = gi % Cfg::kQStages;
@@ -634,7 +659,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             kt = w.kt;
             n_left = w.n_iter;
             n_qt = w.n_qt;
-            row0 = w.qt0 * kTile + warp * 32;  // first query position of this warp's slice in the item's lowest tile
+            row0 = w.y0 + w.qt0 * kTile + warp * 32;  // first query position of this warp's slice in the item's lowest tile
             row = q_y_of(w, 0) + warp * 32;    // ... and in the tile its loop starts with
             wz = ws_z_of(w, 0);
         }
@@ -690,21 +715,35 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             } else {
     #pragma unroll 1
                 for (int rnd = 0; rnd < kRounds; ++rnd) {
-    // (unrolled on purpose: with both boxes in flight the role wants 110 registers and spills ~100 bytes under the
-    // kernel's 80, but the rolled loop, which fits, makes the drain the slowest role: measured 10 % slower)
+                    // 16-column chunks, the load of the next chunk in flight while this one is staged: two chunks
+                    // (32 registers) live.  With whole 32-column boxes in flight the role wanted 110 registers and
+                    // spilled ~100 bytes per thread under the kernel's 80 (4 % of the SM's load/store wavefronts, on
+                    // the pipe that bounds the kernel); loading one box at a time without overlap fitted but made the
+                    // drain the slowest role (10 % slower).
+                    constexpr int kChunks = Cfg::kDqBoxes * 2;
+                    // (row base with the lane's swizzle term in bits 4-6: the address of 16-byte chunk c of the row is
+                    // the base XOR c << 4, one instruction per store; made opaque per iteration, because the compiler
+                    // otherwise keeps all sixteen addresses in registers across the loop)
+                    const uint32_t stage_sw = opaque_u32(smem_u32(stage) | ((uint32_t)sw << 4));
+                    auto stage16 = [&](const uint32_t (&v)[16], int ck) {  // chunk ck of the round: box ck / 2, half ck % 2
     #pragma unroll
-                    for (int bx = 0; bx < Cfg::kDqBoxes; ++bx) {
-                        uint32_t v[32];
-                        tmem_ld32(tDQ + (rnd * Cfg::kDqBoxes + bx) * 32, v);
-                        tmem_wait_ld();
-                        if (rnd == kRounds - 1 && bx == Cfg::kDqBoxes - 1) {  // every column is in registers: hand the TMEM tile back
+                        for (int c4 = 0; c4 < 4; ++c4)
+                            st_shared_v4((stage_sw + (ck >> 1) * 4096) ^ (((ck & 1) * 4 + c4) << 4), v[4 * c4], v[4 * c4 + 1],
+                                         v[4 * c4 + 2], v[4 * c4 + 3]);
+                    };
+                    uint32_t va[16], vb[16];
+                    const uint32_t t0 = tDQ + rnd * Cfg::kDqBoxes * 32;
+                    tmem_ld16(t0, va);
+    #pragma unroll
+                    for (int ck = 0; ck < kChunks; ++ck) {
+                        tmem_wait_ld();  // chunk ck has arrived
+                        if (ck + 1 < kChunks) {
+                            if (ck & 1) tmem_ld16(t0 + (ck + 1) * 16, va); else tmem_ld16(t0 + (ck + 1) * 16, vb);
+                        } else if (rnd == kRounds - 1) {  // every column is in registers: hand the TMEM tile back
                             tc_fence_before_sync();
                             mbar_arrive(dq_empty);
                         }
-    #pragma unroll
-                        for (int c8 = 0; c8 < 8; ++c8)
-                            *reinterpret_cast<uint4*>(stage + bx * 4096 + ((c8 ^ sw) << 4)) =
-                                make_uint4(v[4 * c8], v[4 * c8 + 1], v[4 * c8 + 2], v[4 * c8 + 3]);
+                        if (ck & 1) stage16(vb, ck); else stage16(va, ck);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -765,19 +804,28 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         uint32_t pk_cur[C / 2];  // P^T(it) of this thread: C query columns as packed bf16 pairs
 
         // P^T of 16 columns [16*hf, 16*hf+16) from the S^T values v (which already hold S - LSE/scale) -> packed pairs
-        auto p_half = [&](const uint32_t (&v)[16], int hf, bool masked, uint32_t* out) {
+        // (masked: the query columns outside [c_lo, c_hi) of this key row are zeroed: c_lo = j on the causal diagonal
+        // tile; packed batches also cut at the end of the sequence, in the query and in the key direction)
+        auto p_half = [&](const uint32_t (&v)[16], int hf, bool masked, int c_lo, int c_hi, uint32_t* out) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float e0 = ex2_approx(__uint_as_float(v[4 * i + 0]) * c);
                 float e1 = ex2_approx(__uint_as_float(v[4 * i + 1]) * c);
                 float e2 = ex2_approx(__uint_as_float(v[4 * i + 2]) * c);
                 float e3 = ex2_approx(__uint_as_float(v[4 * i + 3]) * c);
-                if (masked) {  // key j is visible to query i iff j <= i
+                if (masked) {
                     const int col = w * C + hf * 16 + 4 * i;
-                    if (j > col + 0) e0 = 0.f;
-                    if (j > col + 1) e1 = 0.f;
-                    if (j > col + 2) e2 = 0.f;
-                    if (j > col + 3) e3 = 0.f;
+                    if constexpr (kVarlen) {
+                        if (col + 0 < c_lo || col + 0 >= c_hi) e0 = 0.f;
+                        if (col + 1 < c_lo || col + 1 >= c_hi) e1 = 0.f;
+                        if (col + 2 < c_lo || col + 2 >= c_hi) e2 = 0.f;
+                        if (col + 3 < c_lo || col + 3 >= c_hi) e3 = 0.f;
+                    } else {  // causal diagonal tile: key j is visible to query i iff j <= i
+                        if (j > col + 0) e0 = 0.f;
+                        if (j > col + 1) e1 = 0.f;
+                        if (j > col + 2) e2 = 0.f;
+                        if (j > col + 3) e3 = 0.f;
+                    }
                 }
                 out[2 * i + 0] = pack_bf16x2(e0, e1);
                 out[2 * i + 1] = pack_bf16x2(e2, e3);
@@ -826,7 +874,16 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         };
 
         // S^T(g) -> P^T(g), published for dV
-        auto make_p = [&](int g, bool masked) -> bool {
+        // diag: the tile on the causal diagonal; q_valid / kv_valid: query columns / key rows of the tile pair that
+        // belong to the sequence (packed batches only; >= kTile when the tile is whole)
+        auto make_p = [&](int g, bool diag, int q_valid, int kv_valid) -> bool {
+            bool masked = diag;
+            int c_lo = 0, c_hi = kTile;
+            if constexpr (kVarlen) {
+                masked = diag || q_valid < kTile || kv_valid < kTile;
+                c_lo = diag ? j : 0;
+                c_hi = (j < kv_valid) ? q_valid : 0;
+            }
             if (!mbar_wait(&s_full[g % Cfg::kQStages], (g / Cfg::kQStages) & 1, ctx, 51)) return false;
             tc_fence_after_sync();
             if (trace_me) GQA_TRACE(0, g - 1, 2);
@@ -835,7 +892,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 uint32_t vs[16];
                 tmem_ld16(tS + hf * 16, vs);
                 tmem_wait_ld();
-                p_half(vs, hf, masked, pk_cur + hf * 8);
+                p_half(vs, hf, masked, c_lo, c_hi, pk_cur + hf * 8);
             }
             if constexpr (!Cfg::kPAliasesS) {
                 if (g > 0) {  // dV(g-1) has consumed P^T(g-1): its columns can be rewritten
@@ -857,10 +914,10 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             tc_fence_after_sync();
             // key rows beyond the end of the sequence are not stored (the TMEM loads below are warp-wide
             // instructions: every lane runs them, only the stores are guarded)
-            const bool row_ok = wi.kt * kTile + j < p.S;
+            const bool row_ok = wi.kt * kTile + j < wi.len;
             constexpr int kQuarter = D / Cfg::kEwGroups;  // columns of dV / dK per warpgroup
             // element offset of this key row in dK / dV
-            const size_t kv_pos = (size_t)wi.kt * kTile + j;
+            const size_t kv_pos = (size_t)wi.y0 + wi.kt * kTile + j;
             const size_t kv_elem = p.bshd ? (((size_t)wi.b * p.S + kv_pos) * p.Hkv + wi.hkv) * D
                                           : (((size_t)wi.b * p.Hkv + wi.hkv) * p.S + kv_pos) * p.d_real;
 #pragma unroll 1
@@ -906,16 +963,22 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         int gi = 0;  // iteration index over all items of this block
         for (int jj = 0; ok; ++jj) {
             int n_iter, n_qt;
+            int kv_valid = kTile, q_tail = kTile;  // packed batches: key rows of the KV tile / query rows of the
+                                                   // sequence's last query tile that belong to the sequence
             {
                 const int idx = fetch_item(jj);
                 if (idx < 0) break;
                 const WorkItem wi = decode(idx);
                 n_iter = wi.n_iter;
                 n_qt = wi.n_qt;
+                if constexpr (kVarlen) {
+                    kv_valid = wi.len - wi.kt * kTile;
+                    q_tail = wi.len - (wi.qt0 + wi.n_qt - 1) * kTile;
+                }
                 if (warp == kWarpEw0 && lane == 0) GQA_ITEM_BEGIN(idx);
             }
             // ---- prologue: P^T of the item's first iteration (the diagonal tile when causal)
-            ok = make_p(gi, p.causal != 0);
+            ok = make_p(gi, p.causal != 0, n_qt == 1 ? q_tail : kTile, kv_valid);
             if (trace_me) GQA_MARK(2);
             for (int it = 0; it < n_iter && ok; ++it, ++gi) {
                 // ---- dS^T(it) from dP^T(it) and the P^T(it) kept in registers
@@ -948,7 +1011,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 if (trace_me) GQA_TRACE(0, gi, 1);
                 if (it + 1 == n_iter) continue;
                 // ---- P^T(it+1) from S^T(it+1)
-                ok = make_p(gi + 1, p.causal && ((it + 1) % n_qt == 0));
+                const int qi = (it + 1) % n_qt;  // position of the next tile in its query head
+                ok = make_p(gi + 1, p.causal && qi == 0, qi == n_qt - 1 ? q_tail : kTile, kv_valid);
             }
             // ---- epilogue, before the next item's first P^T: the issuers need the accumulators back for its products
             if (ok) ok = epilogue(jj);
@@ -1025,7 +1089,11 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
         rc = make_f32box3_tmap(&mdq, dq_accum, D, S, nws, 32);
         if (rc) return rc;
     }
-    auto kernel = dq_accum ? gqa_bwd_sm100_kernel<D, true> : gqa_bwd_sm100_kernel<D, false>;
+    const bool varlen = s.cu_seqlens != nullptr;
+    if (varlen && (!dq_accum || dq_turn || parts != 1 || !s.bshd || s.B != 1)) return GQA_ERR_BAD_ARGUMENT;
+    auto kernel = varlen     ? gqa_bwd_sm100_kernel<D, true, true>
+                  : dq_accum ? gqa_bwd_sm100_kernel<D, true, false>
+                             : gqa_bwd_sm100_kernel<D, false, false>;
     GQA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemTotal));
     BwdParams p;
     p.dq_accum = dq_accum;
@@ -1041,11 +1109,13 @@ int launch_bwd_t(const void* Q, const void* K, const void* V, const void* dO, co
     p.causal = s.causal;
     p.bshd = s.bshd;
     p.d_real = s.D;
-    p.n_tiles = (s.S + kTile - 1) / kTile;
+    p.cu = s.cu_seqlens;
+    // packed batch: the item list is laid out for max_seqlen; the kernel skips what lies beyond a sequence
+    p.n_tiles = ((varlen ? s.max_seqlen : s.S) + kTile - 1) / kTile;
     p.G = s.G();
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
-    p.groups = s.B * s.Hkv;
+    p.groups = (varlen ? s.n_seqs : s.B) * s.Hkv;
     p.sg = dq_turn ? p.groups : causal_super_group(p.groups, p.n_tiles, resident_blocks());
     p.n_items = p.n_tiles * p.groups * parts;
     // persistent, except in the deterministic mode (see the work-item comment in the kernel)

@@ -70,6 +70,7 @@ struct FwdParams {
     float* LSE;
     unsigned int* status;
     int Hq, Hkv, S, causal, n_pairs, bshd;
+    const int* cu;     // packed variable-length batch: sequence starts (blockIdx.z = sequence), else null
     int d_real;        // head dimension of the tensors (<= D of the kernel; the columns beyond it read as zeros)
     float scale_log2;  // scale * log2(e)
 };
@@ -107,16 +108,27 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 
     // ---- work decode ------------------------------------------------------------
     const int pair = p.causal ? (p.n_pairs - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // heavy causal tiles first
-    const int hq = blockIdx.y, b = blockIdx.z;
+    const int hq = blockIdx.y;
     const int hkv = hq / (p.Hq / p.Hkv);
     const int q0 = pair * 2 * kTile;
-    const int n_tiles = (q0 + kTile < p.S) ? 2 : 1;
-    const int n_blocks_all = (p.S + kTile - 1) / kTile;  // the last block may be partial: keys at and beyond S are masked
+    // Packed variable-length batch: the sequence is a row range [y0, y0 + len) of the one [T, H*D] matrix; rows past
+    // its end belong to the next sequence (or read as zeros past T): as keys they are masked like keys beyond S,
+    // as queries they are computed and not stored.  The grid covers max_seqlen: blocks beyond this sequence leave
+    // here, before anything is set up.
+    int b = blockIdx.z, y0 = 0, len = p.S;
+    if (p.cu) {
+        y0 = p.cu[b];
+        len = p.cu[b + 1] - y0;
+        b = 0;
+        if (q0 >= len) return;
+    }
+    const int n_tiles = (q0 + kTile < len) ? 2 : 1;
+    const int n_blocks_all = (len + kTile - 1) / kTile;  // the last block may be partial: keys at and beyond len are masked
     int n_blk[2];
     n_blk[0] = p.causal ? (q0 / kTile + 1) : n_blocks_all;
     n_blk[1] = (n_tiles == 2) ? (p.causal ? (q0 / kTile + 2) : n_blocks_all) : 0;
     const int n_max = n_blk[1] > n_blk[0] ? n_blk[1] : n_blk[0];
-    const int q_row0 = (b * p.Hq + hq) * p.S + q0;   // row in [B,Hq,S] order (LSE)
+    const int q_row0 = (b * p.Hq + hq) * p.S + y0 + q0;   // row in [B,Hq,S] order (LSE)
     // Tensor-map coordinates (x = column, y = position in the sequence, z = matrix).  [B,H,S,D] is B*H matrices
     // [S, D]; [B,S,H,D] is B matrices [S, H*D] with the head at x = head * D.  Rows at y >= S read as zeros.
     const int q_x = p.bshd ? hq * D : 0, q_z = p.bshd ? b : b * p.Hq + hq;
@@ -166,7 +178,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             for (int t = 0; t < n_tiles; ++t) {
                 mbar_expect_tx(&q_full[t], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_3d(sQ + t * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[t], q_x + pn * 64, q0 + t * kTile, q_z);
+                    tma_load_3d(sQ + t * Cfg::kTileBytes + pn * kPanel, &mapQ, &q_full[t], q_x + pn * 64, y0 + q0 + t * kTile, q_z);
             }
             for (int n = 0; n < n_max; ++n) {
                 const int st = n % Cfg::kStages;
@@ -174,11 +186,11 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 if (use > 0 && !mbar_wait(&k_empty[st], (use - 1) & 1, ctx, 10)) break;
                 mbar_expect_tx(&k_full[st], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_3d(sK + st * Cfg::kTileBytes + pn * kPanel, &mapK, &k_full[st], kv_x + pn * 64, n * kTile, kv_z);
+                    tma_load_3d(sK + st * Cfg::kTileBytes + pn * kPanel, &mapK, &k_full[st], kv_x + pn * 64, y0 + n * kTile, kv_z);
                 if (use > 0 && !mbar_wait(&v_empty[st], (use - 1) & 1, ctx, 11)) break;
                 mbar_expect_tx(&v_full[st], Cfg::kTileBytes);
                 for (int pn = 0; pn < Cfg::kPanels; ++pn)
-                    tma_load_3d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], kv_x + pn * 64, n * kTile, kv_z);
+                    tma_load_3d(sV + st * Cfg::kTileBytes + pn * kPanel, &mapV, &v_full[st], kv_x + pn * 64, y0 + n * kTile, kv_z);
             }
         }
     } else if (warp >= kWarpMma0) {
@@ -260,7 +272,7 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 if (t == 0) GQA_FTRACE(4, j, warp & 3);
                 // last valid column of this row inside the 128-key block: the causal diagonal and / or the end of S
                 const bool diag = p.causal && (n == diag_block);
-                const int s_left = p.S - n * kTile;  // keys of this block that exist
+                const int s_left = len - n * kTile;  // keys of this block that exist
                 const bool masked = diag || s_left < kTile;
                 const int lim = min(diag ? r : kTile - 1, s_left - 1);
                 const int col0 = h * kHalf;  // column of v[0] inside the 128-key block
@@ -367,10 +379,10 @@ gqa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 tc_fence_after_sync();
                 // rows beyond the end of the sequence are not stored (the TMEM loads below are warp-wide
                 // instructions: every lane runs them, only the stores are guarded)
-                const bool row_ok = q0 + t * kTile + r < p.S;
+                const bool row_ok = q0 + t * kTile + r < len;
                 const float inv_l = 1.0f / l_run;
                 const size_t grow_ = (size_t)q_row0 + t * kTile + r;
-                __nv_bfloat16* orow = p.bshd ? p.O + ((size_t)(b * p.S + q0 + t * kTile + r) * p.Hq + hq) * D
+                __nv_bfloat16* orow = p.bshd ? p.O + ((size_t)(b * p.S + y0 + q0 + t * kTile + r) * p.Hq + hq) * D
                                              : p.O + grow_ * p.d_real;
 #pragma unroll 1
                 for (int ch = 0; ch < D / 32; ++ch) {
@@ -428,9 +440,10 @@ int launch_fwd_t(const void* Q, const void* K, const void* V, void* O, float* LS
     p.causal = s.causal;
     p.bshd = s.bshd;
     p.d_real = s.D;
-    p.n_pairs = (s.S + 2 * kTile - 1) / (2 * kTile);
+    p.cu = s.cu_seqlens;
+    p.n_pairs = ((s.cu_seqlens ? s.max_seqlen : s.S) + 2 * kTile - 1) / (2 * kTile);
     p.scale_log2 = s.scale * kLog2e;
-    dim3 grid(p.n_pairs, s.Hq, s.B);
+    dim3 grid(p.n_pairs, s.Hq, s.cu_seqlens ? s.n_seqs : s.B);
     gqa_fwd_sm100_kernel<D><<<grid, kFwdThreads, Cfg::kSmemTotal, stream>>>(mq, mk, mv, p);
     count_launch();
     GQA_CUDA_TRY(cudaGetLastError());

@@ -12,6 +12,11 @@ struct Shape {
     // 0: Q,O,dO,dQ [B,Hq,S,D] and K,V,dK,dV [B,Hkv,S,D] (the reference's layout); 1: [B,S,H,D] for all of them.
     // LSE and the workspace arrays are always in [B,Hq,S] row order.
     int bshd = 0;
+    // Variable-length batch (packed): B = 1, S = the total number of tokens, bshd = 1, i.e. Q [T,Hq,D], K/V [T,Hkv,D],
+    // LSE [Hq,T]; sequence i owns the rows cu_seqlens[i] .. cu_seqlens[i+1]-1 (n_seqs + 1 int32 in device memory)
+    // and attends only to itself; max_seqlen bounds every length (it sizes the grid).
+    const int* cu_seqlens = nullptr;
+    int n_seqs = 0, max_seqlen = 0;
     int G() const { return Hq / Hkv; }
     // Head dimensions other than 64 and 128 run on the kernel of the next size up: the tensor maps describe the real
     // D columns, the 64-column boxes read zeros beyond them (out-of-bounds fill), zero columns add nothing to any

@@ -131,6 +131,79 @@ def gqa_backward(q, k, v, o, do, lse, causal: bool = False, scale: float | None 
     return dq, dk, dv
 
 
+def _packed_dims(q, k, cu_seqlens, max_seqlen):
+    """Shapes of a packed variable-length batch: q [T,Hq,D], k [T,Hkv,D], cu_seqlens int32 [n_seqs+1] on the device."""
+    if q.dim() != 3 or k.dim() != 3:
+        raise ValueError("packed batches are [total_tokens, H, D]")
+    T, Hq, D = q.shape
+    if k.shape[0] != T or k.shape[2] != D:
+        raise ValueError(f"K {tuple(k.shape)} does not match Q {tuple(q.shape)}")
+    if (cu_seqlens.dtype != torch.int32 or cu_seqlens.dim() != 1 or cu_seqlens.numel() < 2 or not cu_seqlens.is_cuda
+            or cu_seqlens.device != q.device or not cu_seqlens.is_contiguous()):
+        raise ValueError(f"cu_seqlens must be a contiguous int32 vector of n_seqs + 1 entries on {q.device}")
+    return T, Hq, k.shape[1], D, cu_seqlens.numel() - 1, int(max_seqlen)
+
+
+def gqa_forward_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = False, scale: float | None = None,
+                       out=None, lse=None, stream=None):
+    """O [T,Hq,D] and LSE [Hq,T] of a packed variable-length batch (``gqa_fwd_varlen``): sequence i is the rows
+    cu_seqlens[i] .. cu_seqlens[i+1]-1 of q [T,Hq,D] and k, v [T,Hkv,D] and attends only to itself."""
+    lib = capi.load_library()
+    for t, n in ((q, "Q"), (k, "K"), (v, "V")):
+        _req(t, n, torch.bfloat16)
+    T, Hq, Hkv, D, n_seqs, max_seqlen = _packed_dims(q, k, cu_seqlens, max_seqlen)
+    _req_like(v, "V", k)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    out = torch.empty_like(q) if out is None else out
+    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device) if lse is None else lse
+    _req_like(out, "O", q)
+    _req_like(lse, "LSE", q, shape=(Hq, T), dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        rc = lib.gqa_fwd_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                cu_seqlens.data_ptr(), n_seqs, T, max_seqlen, Hq, Hkv, D, int(bool(causal)), scale,
+                                _stream_ptr(stream))
+    capi.check("gqa_fwd_varlen", rc)
+    return out, lse
+
+
+def bwd_varlen_workspace_bytes(total_tokens, Hq, Hkv, D) -> int:
+    return int(capi.load_library().gqa_bwd_varlen_workspace_bytes(total_tokens, Hq, Hkv, D))
+
+
+def gqa_backward_varlen(q, k, v, o, do, lse, cu_seqlens, max_seqlen: int, causal: bool = False,
+                        scale: float | None = None, workspace=None, dq=None, dk=None, dv=None, stream=None):
+    """dQ, dK, dV of a packed variable-length batch (``gqa_bwd_varlen``); tensors as in gqa_forward_varlen."""
+    lib = capi.load_library()
+    for t, n in ((q, "Q"), (k, "K"), (v, "V"), (o, "O"), (do, "dO")):
+        _req(t, n, torch.bfloat16)
+    _req(lse, "LSE", torch.float32)
+    T, Hq, Hkv, D, n_seqs, max_seqlen = _packed_dims(q, k, cu_seqlens, max_seqlen)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    need = bwd_varlen_workspace_bytes(T, Hq, Hkv, D)
+    if need == 0:
+        capi.check("gqa_bwd_varlen_workspace_bytes", -2)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    _req_like(v, "V", k)
+    for t, n in ((o, "O"), (do, "dO"), (dq, "dQ")):
+        _req_like(t, n, q)
+    for t, n in ((dk, "dK"), (dv, "dV")):
+        _req_like(t, n, k)
+    _req_like(lse, "LSE", q, shape=(Hq, T), dtype=torch.float32)
+    if not workspace.is_cuda or workspace.device != q.device or not workspace.is_contiguous():
+        raise ValueError(f"workspace must be contiguous memory on {q.device}")
+    with torch.cuda.device(q.device):
+        rc = lib.gqa_bwd_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_seqlens.data_ptr(), n_seqs, T,
+                                max_seqlen, Hq, Hkv, D, int(bool(causal)), scale, workspace.data_ptr(),
+                                workspace.numel() * workspace.element_size(), _stream_ptr(stream))
+    capi.check("gqa_bwd_varlen", rc)
+    return dq, dk, dv
+
+
 def bwd_stage_times(q, k, v, o, do, lse, causal, scale, workspace, dq, dk, dv, flush=None):
     """One backward with events around its stages; returns (preprocess_ms, main_ms, finalise_ms).
     `flush`, if given, is overwritten first so the working set starts outside L2."""

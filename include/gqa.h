@@ -168,6 +168,31 @@ int gqa_bwd_static_scratch(const void* Q, const void* K, const void* V, const vo
                            gqa_stream_t stream);
 
 /*
+ * Packed variable-length batches (no counterpart in the reference, whose kernels take one S for the whole batch:
+ * src/attention/GQA_bwd_baseline.cu:549-554; listed among the shape generalisations a drop-in should add).
+ * n_seqs sequences of different lengths lie back to back, sequence-major: Q, O, dO, dQ are [total_tokens, Hq, D],
+ * K, V, dK, dV [total_tokens, Hkv, D], LSE [Hq, total_tokens]; sequence i owns the rows cu_seqlens[i] ..
+ * cu_seqlens[i+1]-1 and attends only to itself (causal: inside the sequence).  cu_seqlens is n_seqs + 1 int32 in
+ * DEVICE memory, cu_seqlens[0] = 0, non-decreasing, cu_seqlens[n_seqs] = total_tokens; max_seqlen must be at least
+ * the longest length (it sizes the launch; a larger value only costs empty thread blocks).  The library reads
+ * cu_seqlens on the device only, so it cannot check these rules: a longer sequence than max_seqlen is silently
+ * truncated in the forward and loses KV tiles in the backward.  Empty sequences are allowed.  D = 64 or 128.
+ * The tiles of a sequence are fetched at its row offset through the same tensor maps as GQA_LAYOUT_BSHD with B = 1;
+ * rows beyond the end of a sequence (the next sequence's) are masked in the kernels.
+ * gqa_bwd_varlen takes a workspace of gqa_bwd_varlen_workspace_bytes(...) bytes under the rules of gqa_bwd; dK and
+ * dV are bit-reproducible, dQ is summed by fp32 reduce-add operations (no ordered mode for packed batches).
+ */
+int gqa_fwd_varlen(const void* Q, const void* K, const void* V, void* O, float* LSE,
+                   const int* cu_seqlens, int n_seqs, int total_tokens, int max_seqlen,
+                   int Hq, int Hkv, int D, int causal, float scale, gqa_stream_t stream);
+size_t gqa_bwd_varlen_workspace_bytes(int total_tokens, int Hq, int Hkv, int D);
+int gqa_bwd_varlen(const void* Q, const void* K, const void* V, const void* O, const void* dO,
+                   const float* LSE, void* dQ, void* dK, void* dV,
+                   const int* cu_seqlens, int n_seqs, int total_tokens, int max_seqlen,
+                   int Hq, int Hkv, int D, int causal, float scale,
+                   void* workspace, size_t workspace_bytes, gqa_stream_t stream);
+
+/*
  * gqa_bwd with CUDA events recorded on `stream` around its three stages.  Fills
  * stage_ms[0..2] (host memory) with the device time of the Delta preprocess, the
  * tensor-core main kernel and the dQ finalise, and synchronises the stream.  The
