@@ -30,6 +30,7 @@ from __future__ import annotations
 
 import argparse
 import datetime
+import itertools
 import json
 import math
 import os
@@ -264,6 +265,30 @@ def other_configs(gqa, ops, dev, timer, peaks):
     fwd_bwd("headline_shape_causal", 8, 12, 4, 4096, 64, True)
     fwd_bwd("causal_d128", 4, 32, 8, 8192, 128, True, do_mul=0.1)
     fwd_bwd("long_context", 1, 64, 8, 32768, 128, True)
+    # a packed variable-length batch: 32 768 tokens in sequences of 128 .. 8 192 (two thirds of them short), causal
+    lens = [8192, 4096, 4096, 2048, 2048, 2048, 1024, 1024, 1024, 1024] + [512] * 8 + [256] * 6 + [128] * 4
+    T, Hq, Hkv, D = sum(lens), 32, 8, 128
+    g = torch.Generator(device=dev).manual_seed(13)
+    q = torch.randn(T, Hq, D, generator=g, device=dev).bfloat16()
+    k = torch.randn(T, Hkv, D, generator=g, device=dev).bfloat16()
+    v = torch.randn(T, Hkv, D, generator=g, device=dev).bfloat16()
+    do = (torch.randn(T, Hq, D, generator=g, device=dev) * 0.1).bfloat16()
+    cu = torch.tensor([0] + list(itertools.accumulate(lens)), dtype=torch.int32, device=dev)
+    o, lse = torch.empty_like(q), torch.empty(Hq, T, dtype=torch.float32, device=dev)
+    f_ms = timer(lambda: ops.gqa_forward_varlen(q, k, v, cu, max(lens), causal=True, out=o, lse=lse))
+    ops.check_status()
+    ws = torch.empty(ops.bwd_varlen_workspace_bytes(T, Hq, Hkv, D), dtype=torch.uint8, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    b_ms = timer(lambda: ops.gqa_backward_varlen(q, k, v, o, do, lse, cu, max(lens), causal=True, workspace=ws, dq=dq,
+                                                 dk=dk, dv=dv))
+    ops.check_status(ws)
+    f_fl = sum(fwd_flops(1, Hq, n, D, True) for n in lens)
+    out["packed_varlen_causal_d128"] = {
+        "shape": f"{len(lens)} sequences of 128..8192 tokens, {T} in all, Hq{Hq} Hkv{Hkv} D{D} causal, [T,H,D] + cu_seqlens",
+        "fwd": rate(f_fl, f_ms, peaks, 1.0), "bwd": rate(4.0 * f_fl, b_ms, peaks, 10.0 / 16.0),
+        "outputs_finite": bool(torch.isfinite(dq.float()).all() and torch.isfinite(dk.float()).all()
+                               and torch.isfinite(dv.float()).all() and torch.isfinite(o.float()).all())}
+    del q, k, v, do, o, lse, ws, dq, dk, dv
     sweep = {}
     for D in (64, 128):
         for S in (1024, 2048, 4096, 16384):

@@ -83,7 +83,7 @@ __device__ __forceinline__ int trace_smid() {
     } while (0)
 #define GQA_TRACE(role, it, slot)                                                                  \
     do {                                                                                           \
-        if (blockIdx.x == GQA_BWD_TRACE_BLOCK && (it) < 64 && (threadIdx.x & 31) == 0) g_bwd_trace[role][it][slot] = clock64(); \
+        if (blockIdx.x == GQA_BWD_TRACE_BLOCK && (it) >= 0 && (it) < 64 && (threadIdx.x & 31) == 0) g_bwd_trace[role][it][slot] = clock64(); \
     } while (0)
 #else
 #define GQA_TRACE(role, it, slot) \
@@ -715,35 +715,24 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             } else {
     #pragma unroll 1
                 for (int rnd = 0; rnd < kRounds; ++rnd) {
-                    // 16-column chunks, the load of the next chunk in flight while this one is staged: two chunks
-                    // (32 registers) live.  With whole 32-column boxes in flight the role wanted 110 registers and
-                    // spilled ~100 bytes per thread under the kernel's 80 (4 % of the SM's load/store wavefronts, on
-                    // the pipe that bounds the kernel); loading one box at a time without overlap fitted but made the
-                    // drain the slowest role (10 % slower).
-                    constexpr int kChunks = Cfg::kDqBoxes * 2;
-                    // (row base with the lane's swizzle term in bits 4-6: the address of 16-byte chunk c of the row is
-                    // the base XOR c << 4, one instruction per store; made opaque per iteration, because the compiler
-                    // otherwise keeps all sixteen addresses in registers across the loop)
-                    const uint32_t stage_sw = opaque_u32(smem_u32(stage) | ((uint32_t)sw << 4));
-                    auto stage16 = [&](const uint32_t (&v)[16], int ck) {  // chunk ck of the round: box ck / 2, half ck % 2
+                    // (Plain stores whose order against the TMEM loads is left to the compiler.  Measured alternatives,
+                    // all slower at D = 64 although they remove the ~100 bytes per thread that this form spills under the
+                    // kernel's 80 registers: the box loop not unrolled, 10 %; 16-column chunks with the next load in
+                    // flight, 1-3 %; the second box's load issued by hand before the first box is staged, 4 %; the same
+                    // boxes with the staging addresses recomputed per tile pair instead of kept in registers, 0.7 %.)
     #pragma unroll
-                        for (int c4 = 0; c4 < 4; ++c4)
-                            st_shared_v4((stage_sw + (ck >> 1) * 4096) ^ (((ck & 1) * 4 + c4) << 4), v[4 * c4], v[4 * c4 + 1],
-                                         v[4 * c4 + 2], v[4 * c4 + 3]);
-                    };
-                    uint32_t va[16], vb[16];
-                    const uint32_t t0 = tDQ + rnd * Cfg::kDqBoxes * 32;
-                    tmem_ld16(t0, va);
-    #pragma unroll
-                    for (int ck = 0; ck < kChunks; ++ck) {
-                        tmem_wait_ld();  // chunk ck has arrived
-                        if (ck + 1 < kChunks) {
-                            if (ck & 1) tmem_ld16(t0 + (ck + 1) * 16, va); else tmem_ld16(t0 + (ck + 1) * 16, vb);
-                        } else if (rnd == kRounds - 1) {  // every column is in registers: hand the TMEM tile back
+                    for (int bx = 0; bx < Cfg::kDqBoxes; ++bx) {
+                        uint32_t v[32];
+                        tmem_ld32(tDQ + (rnd * Cfg::kDqBoxes + bx) * 32, v);
+                        tmem_wait_ld();
+                        if (rnd == kRounds - 1 && bx == Cfg::kDqBoxes - 1) {  // every column is in registers: hand the TMEM tile back
                             tc_fence_before_sync();
                             mbar_arrive(dq_empty);
                         }
-                        if (ck & 1) stage16(vb, ck); else stage16(va, ck);
+    #pragma unroll
+                        for (int c8 = 0; c8 < 8; ++c8)
+                            *reinterpret_cast<uint4*>(stage + bx * 4096 + ((c8 ^ sw) << 4)) =
+                                make_uint4(v[4 * c8], v[4 * c8 + 1], v[4 * c8 + 2], v[4 * c8 + 3]);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -784,9 +773,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         }
     } else if (warp < Cfg::kWarpTma) {
         // ======================= elementwise warpgroups (P^T and dS^T) =======================
-        // Rotated by half an iteration: the body of iteration `it` turns dP^T(it) into dS^T(it) and then
-        // S^T(it+1) into P^T(it+1); P^T is carried in registers as packed bf16 (the rounded values the
-        // dV product uses) between the two halves.
+        // Per tile pair: S^T(it) -> P^T(it), then dP^T(it) -> dS^T(it); P^T is carried in registers as packed bf16
+        // (the rounded values the dV product uses) between the two phases.
         constexpr int C = Cfg::kCols, H = Cfg::kHalves;
         const int w = (warp - kWarpEw0) >> 2;     // which C query columns of the tile pair
         const int j = (warp & 3) * 32 + lane;     // key row inside the tile == TMEM lane
@@ -977,11 +965,14 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 }
                 if (warp == kWarpEw0 && lane == 0) GQA_ITEM_BEGIN(idx);
             }
-            // ---- prologue: P^T of the item's first iteration (the diagonal tile when causal)
-            ok = make_p(gi, p.causal != 0, n_qt == 1 ? q_tail : kTile, kv_valid);
-            if (trace_me) GQA_MARK(2);
+            // One pass per tile pair: P^T(it) from S^T(it), then dS^T(it) from dP^T(it) and the P^T(it) kept in registers.
+            // (One copy of each phase in the instruction stream: this loop is the bulk of the kernel's code, and the
+            // roles of an SM already miss in the instruction cache.)
+            int qi = 0;  // position of the tile in its query head: 0 is the diagonal tile when causal
             for (int it = 0; it < n_iter && ok; ++it, ++gi) {
-                // ---- dS^T(it) from dP^T(it) and the P^T(it) kept in registers
+                ok = make_p(gi, p.causal && qi == 0, qi == n_qt - 1 ? q_tail : kTile, kv_valid);
+                if (++qi == n_qt) qi = 0;
+                if (!ok) break;
                 ok = mbar_wait(&dp_full[gi % Cfg::kDOStages], (gi / Cfg::kDOStages) & 1, ctx, 53);
                 if (ok && gi > 0) ok = mbar_wait(ds_free, (gi - 1) & 1, ctx, 54);  // dK and dQ of the iteration before have read its dS^T
                 if (!ok) break;
@@ -1009,10 +1000,6 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 tc_fence_before_sync();
                 mbar_arrive(ds_ready);
                 if (trace_me) GQA_TRACE(0, gi, 1);
-                if (it + 1 == n_iter) continue;
-                // ---- P^T(it+1) from S^T(it+1)
-                const int qi = (it + 1) % n_qt;  // position of the next tile in its query head
-                ok = make_p(gi + 1, p.causal && qi == 0, qi == n_qt - 1 ? q_tail : kTile, kv_valid);
             }
             // ---- epilogue, before the next item's first P^T: the issuers need the accumulators back for its products
             if (ok) ok = epilogue(jj);

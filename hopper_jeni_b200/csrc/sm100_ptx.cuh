@@ -95,17 +95,6 @@ __device__ __forceinline__ void abort_grace_period() {
     for (int i = 0; i < 4; ++i) __nanosleep(250000);
 }
 
-// 16-byte store to shared memory at a 32-bit shared-window address.
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-// Hides where a value came from, so that address arithmetic built on it is redone where it is used instead of being
-// kept in registers across a long loop.
-__device__ __forceinline__ uint32_t opaque_u32(uint32_t x) {
-    asm volatile("" : "+r"(x));
-    return x;
-}
-
 // ----------------------------------------------------------------------------
 // Fences
 // ----------------------------------------------------------------------------
