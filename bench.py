@@ -372,7 +372,7 @@ def sharded_problem(name, shape, tensors, gqa, ops, sharding, timer, dist, rank,
             "frac_executed_of_measured_burst_per_gpu": round(flops * 10 / 16 / (slow * 1e-3) / 1e12 / world
                                                              / peaks["bf16_tflops"], 3),
             "speedup_vs_one_gpu": round(one_ms / slow, 3), "efficiency": round(one_ms / slow / world, 3),
-            "thread_blocks_per_rank": int(math.ceil(S / 128) * max(e - b for b, e in
+            "work_items_per_rank": int(math.ceil(S / 128) * max(e - b for b, e in
                                                                      (sharding.group_range(r, world, n_groups)
                                                                       for r in range(world)))),
             "gather": "NCCL all_gather of dQ/dK/dV shards" if dist is not None else "single rank (no gather)",

@@ -1,11 +1,13 @@
 // GQA backward, stage 2 of 3, for sm_100a: the KV-tile-parallel main kernel.
 //
-// One CTA owns one 128-row key/value tile of one (batch, KV head) and loops over
+// A work item is one 128-row key/value tile of one (batch, KV head): the thread block that takes it loops over
 // all G query heads of the group and over the 128-row query tiles that see the
 // tile (all of them, or the ones at and below the diagonal when causal).  dK and
 // dV therefore accumulate in tensor memory across the whole GQA group and are
 // written exactly once: no atomics, bit-reproducible.  dQ tiles are reduced into
 // an fp32 accumulator with vector reductions (order-dependent in the last bits).
+// The thread blocks are persistent (one per SM) and claim items from a counter, the work of the reference's
+// persistent launchers with an atomic tile counter (src/attention/GQA_bwd.cu:14269-14278, :14351-14376).
 //
 // Everything is computed in the transposed orientation so that a TMEM lane is a
 // key row:  S^T = K Q^T,  dP^T = V dO^T  (both operands K-major from TMA panels),
