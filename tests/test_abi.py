@@ -82,6 +82,18 @@ def test_argument_validation_needs_no_device(gqa_lib, selftest_lib):
     assert selftest_lib.gqa_selftest_timeout(p, 10 ** 10, 1, None) == -1                           # limit capped
     assert selftest_lib.gqa_selftest_timeout(None, 1000, 1, None) == -1
     assert gqa_lib.gqa_bwd_delta(p, p, p, 16, 36, None) == -2
+    # packed variable-length batches: (..., cu_seqlens, n_seqs, total_tokens, max_seqlen, Hq, Hkv, D, causal, scale, ...)
+    assert gqa_lib.gqa_fwd_varlen(p, p, p, p, None, None, 2, 256, 128, 4, 2, 64, 0, 0.125, None) == -1   # no cu_seqlens
+    assert gqa_lib.gqa_fwd_varlen(p, p, p, p, None, p, 0, 256, 128, 4, 2, 64, 0, 0.125, None) == -1      # n_seqs <= 0
+    assert gqa_lib.gqa_fwd_varlen(p, p, p, p, None, p, 2, 256, 0, 4, 2, 64, 0, 0.125, None) == -1        # max_seqlen <= 0
+    assert gqa_lib.gqa_fwd_varlen(p, p, p, p, None, p, 2, 256, 300, 4, 2, 64, 0, 0.125, None) == -1      # ... > total
+    assert gqa_lib.gqa_fwd_varlen(p, p, p, p, None, mis, 2, 256, 128, 4, 2, 64, 0, 0.125, None) == -1    # misaligned
+    assert gqa_lib.gqa_fwd_varlen(p, p, p, p, None, p, 2, 256, 128, 4, 2, 96, 0, 0.125, None) == -2      # D = 64 / 128 only
+    assert gqa_lib.gqa_fwd_varlen(p, p, p, p, None, p, 2, 256, 128, 5, 2, 64, 0, 0.125, None) == -2      # Hq % Hkv
+    assert gqa_lib.gqa_bwd_varlen(p, p, p, p, p, p, p, p, p, p, 2, 256, 128, 4, 2, 64, 0, 0.125, p, 16, None) == -3
+    assert gqa_lib.gqa_bwd_varlen(p, p, p, p, p, p, p, p, p, None, 2, 256, 128, 4, 2, 64, 0, 0.125, p, 1 << 30, None) == -1
+    assert gqa_lib.gqa_bwd_varlen_workspace_bytes(256, 4, 2, 96) == 0
+    assert gqa_lib.gqa_bwd_varlen_workspace_bytes(256, 4, 2, 64) == gqa_lib.gqa_bwd_workspace_bytes(1, 4, 2, 256, 64, 0)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
