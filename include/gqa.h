@@ -103,11 +103,13 @@ int gqa_bwd(const void* Q, const void* K, const void* V, const void* O, const vo
  * (cp.reduce.async.bulk add, src/attention/GQA_bwd_baseline.cu:360-365, run-to-run differences noted in
  * docs/report.md:115-116) and has no such switch; its determinism probe
  * (precision/vj1d_determinism_probe.cu:33) is what this mode is checked with.  Slower than the default
- * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.  A thread
- * block waits for the turn of the block that owns the previous KV tile of its group, which has a smaller block
- * index: the mode relies on the hardware starting thread blocks in index order (it does on every CUDA GPU so far,
- * but CUDA does not promise it); the wait is bounded, so a violation would end in GQA_ERR_DEVICE_TIMEOUT, not in
- * a hang.
+ * (the thread blocks of one (batch, KV head) group reduce one after the other).  Same workspace size.  This mode
+ * runs one thread block per KV tile (the default mode runs one persistent block per SM): a thread block waits for
+ * the turn of the block that owns the previous KV tile of its group, which has a smaller block index, so the mode
+ * relies on the hardware starting thread blocks in index order (it does on every CUDA GPU so far, but CUDA does
+ * not promise it); the wait is bounded, so a violation would end in GQA_ERR_DEVICE_TIMEOUT, not in a hang.
+ * dK and dV of this mode and of the default mode are each bit-reproducible; without a causal mask they differ from
+ * each other in the last bits (the default mode starts every KV tile's loop over the query tiles at another tile).
  * GQA_LAYOUT_BSHD (see gqa_fwd_ex): Q, O, dO, dQ are [B,S,Hq,D] and K, V, dK, dV [B,S,Hkv,D]; LSE stays [B,Hq,S].
  * Unknown flag bits are refused with GQA_ERR_BAD_ARGUMENT.
  * GQA_BWD_SPLIT_HEADS: for calls with too few KV tiles to fill the GPU evenly (fewer than two per SM: a
@@ -222,7 +224,8 @@ int gqa_bwd_delta(const void* O, const void* dO, float* delta, size_t rows, int 
  * CUDA error: no launch clears it, so forwards running on several streams cannot erase each other's
  * report, and while it is set every later gqa_fwd on that GPU returns without computing (its thread
  * blocks exit at once).  Reading it with this function clears it.  In both kernels a thread block that
- * starts after another one has given up exits immediately, so a wedged launch drains within one wave.
+ * starts after another one has given up exits immediately, and the persistent blocks of the backward stop taking
+ * work once the word is set, so a wedged launch drains within one wait limit.
  * The reference has no such path: its waits spin without limit (src/attention/GQA_bwd_baseline.cu:85-93).
  */
 int gqa_check_status(const void* workspace, gqa_stream_t stream);
