@@ -321,7 +321,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // starting at tile 0, the first waves ran 10-15 % slower per tile pair than the later, drifted-apart ones).
         // Causal blocks are staggered already (block kt starts at query tile kt); the deterministic mode wants its
         // blocks on the same tile one after the other.
-        w.shift = (kt_major || kVarlen) ? 0 : w.kt;
+        w.shift = kt_major ? 0 : w.kt;
         w.kv_x = p.bshd ? w.hkv * D : 0;
         w.kv_z = p.bshd ? w.b : w.b * p.Hkv + w.hkv;
         return w;
@@ -953,6 +953,8 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         int gi = 0;  // iteration index over all items of this block
         for (int jj = 0; ok; ++jj) {
             int n_iter, n_qt;
+            int qi = 0;  // position of the tile pair's query tile in its head: 0 is the diagonal tile when causal, n_qt - 1
+                         // the sequence's last (possibly partial) one; the loop starts at the item's rotation
             int kv_valid = kTile, q_tail = kTile;  // packed batches: key rows of the KV tile / query rows of the
                                                    // sequence's last query tile that belong to the sequence
             {
@@ -961,6 +963,7 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                 const WorkItem wi = decode(idx);
                 n_iter = wi.n_iter;
                 n_qt = wi.n_qt;
+                qi = wi.shift;
                 if constexpr (kVarlen) {
                     kv_valid = wi.len - wi.kt * kTile;
                     q_tail = wi.len - (wi.qt0 + wi.n_qt - 1) * kTile;
@@ -970,7 +973,6 @@ gqa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
             // One pass per tile pair: P^T(it) from S^T(it), then dS^T(it) from dP^T(it) and the P^T(it) kept in registers.
             // (One copy of each phase in the instruction stream: this loop is the bulk of the kernel's code, and the
             // roles of an SM already miss in the instruction cache.)
-            int qi = 0;  // position of the tile in its query head: 0 is the diagonal tile when causal
             for (int it = 0; it < n_iter && ok; ++it, ++gi) {
                 ok = make_p(gi, p.causal && qi == 0, qi == n_qt - 1 ? q_tail : kTile, kv_valid);
                 if (++qi == n_qt) qi = 0;

@@ -134,8 +134,8 @@ def test_varlen_long_sequences_match_fp32_sdpa(gqa_lib, D, causal):
 
 
 def test_varlen_equal_lengths_equal_the_batched_call(gqa_lib):
-    """A packed batch of equal, tile-aligned lengths is the [B,S,H,D] problem: O, LSE bit for bit; with a causal mask
-    dK and dV too (without one the batched call starts its query loops at other tiles: same sums, other order)."""
+    """A packed batch of equal, tile-aligned lengths is the [B,S,H,D] problem: O, LSE, dK and dV bit for bit (same
+    arithmetic in the same order), dQ up to the order of the fp32 reductions."""
     B, Hq, Hkv, S, D = 3, 8, 2, 512, 64
     gen = torch.Generator(device="cuda").manual_seed(23)
     q = torch.randn(B, S, Hq, D, generator=gen, device="cuda").bfloat16()
@@ -155,11 +155,9 @@ def test_varlen_equal_lengths_equal_the_batched_call(gqa_lib):
         ops.check_status(ws)
         dq2, dk2, dv2 = ops.gqa_backward_varlen(q.view(B * S, Hq, D), k.view(B * S, Hkv, D), v.view(B * S, Hkv, D), o2,
                                                 do.view(B * S, Hq, D), lse2, cu, S, causal=causal)
-        if causal:
-            assert torch.equal(dk.view(B * S, Hkv, D), dk2) and torch.equal(dv.view(B * S, Hkv, D), dv2)
-        for got, want in ((dq2, dq.view(B * S, Hq, D)), (dk2, dk.view(B * S, Hkv, D)), (dv2, dv.view(B * S, Hkv, D))):
-            m = util.metrics(util.to_np(got), util.to_np(want))
-            assert m["rel_rms"] < 2e-3, m
+        assert torch.equal(dk.view(B * S, Hkv, D), dk2) and torch.equal(dv.view(B * S, Hkv, D), dv2), causal
+        m = util.metrics(util.to_np(dq2), util.to_np(dq.view(B * S, Hq, D)))
+        assert m["rel_rms"] < 2e-3, m
 
 
 def test_varlen_rejects_bad_arguments(gqa_lib):
